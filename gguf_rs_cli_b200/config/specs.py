@@ -41,9 +41,12 @@ class LayerSpec:
 class Run:
     """One entry of the run order: layer `layer` runs here.  `cache_of` is None when
     this run owns cache storage (if its mixer needs any), or the index of an earlier
-    run whose keys and values this run reads instead of making its own."""
+    run whose keys and values this run reads instead of making its own.  `add_input`: before this run, what the
+    embedding gave for the step's tokens is added to the residual stream once more (a model that runs a stretch of
+    layers several times feeds its input to every pass but the first)."""
     layer: int
     cache_of: Optional[int] = None
+    add_input: bool = False
 
 
 @dataclass(frozen=True)

@@ -38,11 +38,14 @@ struct AdParams {
                                  // the first head_pages entries of the table, in front of the ring
     const __nv_bfloat16* gate;   // [T, nh*hd] rows ldg apart, or null: the result is multiplied by sigmoid(gate)
     long long ldg;
+    int gate_per_head;           // the gate is [T, nh]: one number for all entries of a head's result
+    int sink;                    // the softmax's denominator counts one more key of score 0 that has no value
 };
 
 __device__ __forceinline__ float ad_gated(const AdParams& p, int t, int h, int d, float o) {
     if (!p.gate) return o;
-    return o / (1.f + expf(-__bfloat162float(p.gate[size_t(t) * p.ldg + size_t(h) * p.hd + d])));
+    const size_t at = p.gate_per_head ? size_t(h) : size_t(h) * p.hd + d;
+    return o / (1.f + expf(-__bfloat162float(p.gate[size_t(t) * p.ldg + at])));
 }
 
 __device__ __forceinline__ void unpack8(uint4 v, float* f) {
@@ -214,6 +217,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             o += acc_s[w][gi][d] * wgt;
         }
         if (p.splits == 1) {
+            if (p.sink && M != -INFINITY) L += exp2f(-M);
             p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
         } else {
             float* rec = p.scratch + ((size_t(t) * p.nh + h0 + gi) * p.splits + split) * (hd + 2);
@@ -242,6 +246,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             L += __ldcg(rec + s * (hd + 2) + hd + 1) * wgt;
             o += __ldcg(rec + s * (hd + 2) + d) * wgt;
         }
+        if (p.sink && M != -INFINITY) L += exp2f(-M);
         p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
     }
     if (threadIdx.x == 0) p.counters[t * gridDim.y + ytile] = 0;
@@ -278,7 +283,7 @@ static int attention_decode_launch(const void* q, long long ldq, void* out, long
                                    const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
                                    const void* kcache, const void* vcache, int window, float scale, int splits,
                                    float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
-                                   const void* gate, long long ldg, cudaStream_t stream) {
+                                   const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_decode_supported(hd, GB_BF16, GB_BF16), "gb_attention_decode: head_dim %d must be a multiple of 16 up to 256", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_decode: %d heads are not a multiple of %d KV heads", nh, nkv);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && splits >= 1 && head_pages >= 0, "gb_attention_decode: bad cache geometry");
@@ -296,6 +301,7 @@ static int attention_decode_launch(const void* q, long long ldq, void* out, long
     p.counters = counters; p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.hd = hd; p.table_width = table_width;
     p.ring_pages = ring_pages; p.window = window; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
     p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
+    p.gate_per_head = gate_per_head; p.sink = sink;
     dim3 grid(T, nkv * gtiles, splits);
     int hc = (hd + 63) / 64;
     switch (gt) {
@@ -313,16 +319,18 @@ GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long lon
                                const void* kcache, const void* vcache, int window, float scale, int splits,
                                float* scratch, int* counters, int n_counters, cudaStream_t stream) {
     return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
-                                   window, scale, splits, scratch, counters, n_counters, 0, 0, nullptr, 0, stream);
+                                   window, scale, splits, scratch, counters, n_counters, 0, 0, nullptr, 0, 0, 0, stream);
 }
 
 // The same behind a window that keeps the sequence's first keep_first positions visible (their pages are the first
-// head_pages entries of the page table), the result multiplied by sigmoid(gate) when a gate [T, nh*hd] is given.
+// head_pages entries of the page table), the result multiplied by sigmoid(gate) when a gate [T, nh*hd] (gate_per_head:
+// [T, nh]) is given; sink: one more key of score 0 without a value in the softmax's denominator.
 GB_API int gb_attention_decode_kept(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
                                     const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
                                     const void* kcache, const void* vcache, int window, float scale, int splits,
                                     float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
-                                    const void* gate, long long ldg, cudaStream_t stream) {
+                                    const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
     return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
-                                   window, scale, splits, scratch, counters, n_counters, head_pages, keep_first, gate, ldg, stream);
+                                   window, scale, splits, scratch, counters, n_counters, head_pages, keep_first, gate, ldg,
+                                   gate_per_head, sink, stream);
 }

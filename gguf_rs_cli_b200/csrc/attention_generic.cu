@@ -10,7 +10,8 @@
 // faster kernels in tests, and the path for head sizes those refuse.  Options: the first
 // keep_first positions of a sequence stay visible behind the window (their pages are the
 // first head_pages entries of the page table, in front of the ring); the result is
-// multiplied by sigmoid(gate) entry by entry.
+// multiplied by sigmoid(gate) entry by entry, or by one number per head; the softmax's denominator may count one
+// more key of score 0 that has no value (a sink).
 #include <math.h>
 
 #include "common.cuh"
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     int nh, int nkv, int hd, int hdv, int v_row, const int* __restrict__ seq_of, const int* __restrict__ pos,
     const int* __restrict__ table, int table_width, int ring_pages, const TC* __restrict__ kc,
     const TC* __restrict__ vc, int window, float scale, int head_pages, int keep_first, const void* __restrict__ gate,
-    int gate_dtype, long long ldg) {
+    int gate_dtype, long long ldg, int gate_per_head, int sink) {
     int t = blockIdx.x, h = blockIdx.y;
     int b = seq_of[t];
     size_t orow = size_t(t) * ldo + size_t(h) * hdv;
@@ -161,11 +162,12 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
+    if (sink && M != -INFINITY) L += expf(-M);
     for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < AG_WARPS; ++w) o += acc_s[w][d] * wgt[w];
         o /= L;
-        if (gate) o *= 1.f / (1.f + expf(-gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * hdv + d)));
+        if (gate) o *= 1.f / (1.f + expf(-gb_load(gate, gate_dtype, size_t(t) * ldg + (gate_per_head ? size_t(h) : size_t(h) * hdv + d))));
         gb_store(out, out_dtype, orow + d, o);
     }
 }
@@ -178,7 +180,8 @@ GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void*
                                 int T, int nh, int nkv, int hd, int hdv, int v_row, const int* seq_of, const int* pos,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
                                 const void* vcache, int cache_dtype, int window, float scale, int head_pages, int keep_first,
-                                const void* gate, int gate_dtype, long long ldg, cudaStream_t stream) {
+                                const void* gate, int gate_dtype, long long ldg, int gate_per_head, int sink,
+                                cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(q_dtype) && gb_is_dtype(out_dtype) && gb_is_dtype(cache_dtype), "gb_attention_generic: bad dtype");
     GB_REQUIRE(hd > 0 && hd <= AG_MAX_HD, "gb_attention_generic: head_dim %d is not in 1..%d", hd, AG_MAX_HD);
     GB_REQUIRE(hdv > 0 && hdv <= AG_MAX_HD && v_row >= hdv, "gb_attention_generic: value size %d (rows of %d) is not in 1..%d", hdv, v_row, AG_MAX_HD);
@@ -192,7 +195,7 @@ GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void*
 #define AG_LAUNCH(TC, MAX_HD)                                                                                     \
     attention_generic_kernel<TC, MAX_HD><<<grid, AG_WARPS * 32, 0, stream>>>(                                     \
         q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, hdv, v_row, seq_of, pos, table, table_width, ring_pages, \
-        (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg)
+        (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg, gate_per_head, sink)
     const bool small = hd <= 256 && hdv <= 256;
     if (cache_dtype == GB_F32) {
         if (small) AG_LAUNCH(float, 256);

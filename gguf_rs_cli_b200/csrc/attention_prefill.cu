@@ -45,6 +45,8 @@ struct ApParams {
                                      // the first head_pages entries of the table, in front of the ring
     const __nv_bfloat16* gate;       // [T, nh*HD] or null: the result is multiplied by sigmoid(gate)
     long long ldg;
+    int gate_per_head;               // the gate is [T, nh]: one number for all entries of a head's result
+    int sink;                        // the softmax's denominator counts one more key of score 0 that has no value
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -269,15 +271,24 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (p.sink) {
+        if (m0 != -INFINITY) l0 += exp2f(-m0 * p.scale_log2);
+        if (m1 != -INFINITY) l1 += exp2f(-m1 * p.scale_log2);
+    }
+    float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    const bool entry_gate = p.gate && !p.gate_per_head;
+    if (p.gate && p.gate_per_head) {
+        if (r0 < rows) inv0 *= 1.f / (1.f + expf(-__bfloat162float(p.gate[size_t(tok0 + r0) * p.ldg + h])));
+        if (r1 < rows) inv1 *= 1.f / (1.f + expf(-__bfloat162float(p.gate[size_t(tok0 + r1) * p.ldg + h])));
+    }
     __nv_bfloat16* out0 = p.out + size_t(tok0 + r0) * p.ldo + size_t(h) * HD + 2 * (lane & 3);
     __nv_bfloat16* out1 = p.out + size_t(tok0 + r1) * p.ldo + size_t(h) * HD + 2 * (lane & 3);
-    const __nv_bfloat16* g0 = p.gate ? p.gate + size_t(tok0 + r0) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
-    const __nv_bfloat16* g1 = p.gate ? p.gate + size_t(tok0 + r1) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
+    const __nv_bfloat16* g0 = entry_gate ? p.gate + size_t(tok0 + r0) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
+    const __nv_bfloat16* g1 = entry_gate ? p.gate + size_t(tok0 + r1) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
 #pragma unroll
     for (int i = 0; i < OT; ++i) {
         float2 f0 = make_float2(inv0, inv0), f1 = make_float2(inv1, inv1);
-        if (p.gate) {
+        if (entry_gate) {
             if (r0 < rows) {
                 const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g0 + 8 * i));
                 f0.x *= 1.f / (1.f + expf(-z.x));
@@ -321,13 +332,13 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
                                 const int* tiles, int n_tiles, const int* cu, const int* starts, const int* qlens,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
                                 const void* vcache, int window, float scale, int exact, int head_pages, int keep_first,
-                                const void* gate, long long ldg, cudaStream_t stream) {
+                                const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_prefill_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill: head_dim %d is not 64 or 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
     GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill: %d tiles of queries are too many for one launch", n_tiles);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && head_pages >= 0, "gb_attention_prefill: bad cache geometry");
     GB_REQUIRE(keep_first >= 0, "gb_attention_prefill: a negative number of kept positions");
-    GB_REQUIRE(!gate || ((ldg % 2) == 0 && (reinterpret_cast<uintptr_t>(gate) & 3) == 0), "gb_attention_prefill: misaligned gate");
+    GB_REQUIRE(!gate || gate_per_head || ((ldg % 2) == 0 && (reinterpret_cast<uintptr_t>(gate) & 3) == 0), "gb_attention_prefill: misaligned gate");
     GB_REQUIRE((ldq % 8) == 0 && (ldo % 2) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0,
                "gb_attention_prefill: misaligned operands");
@@ -338,6 +349,7 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
     p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width; p.ring_pages = ring_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
+    p.gate_per_head = gate_per_head; p.sink = sink;
     if (exact) return hd == 64 ? launch_ap<64, true>(p, n_tiles, stream) : launch_ap<128, true>(p, n_tiles, stream);
     return hd == 64 ? launch_ap<64, false>(p, n_tiles, stream) : launch_ap<128, false>(p, n_tiles, stream);
 }

@@ -120,10 +120,11 @@ __device__ __forceinline__ float gb_act_glu_clamped(float g, float u, float limi
     return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
 }
 
-// Activations of one value: 3 GELU in its exact form 0.5 z (1 + erf(z / sqrt 2)); else as gb_gate_act.
-enum GbUnaryAct { GB_ACT_GELU_ERF = 3 };
+// Activations of one value: 3 GELU in its exact form 0.5 z (1 + erf(z / sqrt 2)); 4 tanh; else as gb_gate_act.
+enum GbUnaryAct { GB_ACT_GELU_ERF = 3, GB_ACT_TANH = 4 };
 __device__ __forceinline__ float gb_act_unary(float z, int act) {
     if (act == GB_ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    if (act == GB_ACT_TANH) return tanhf(z);
     return gb_gate_act(z, act);
 }
 

@@ -16,7 +16,8 @@
 __global__ void short_conv_silu_kernel(const void* __restrict__ xin, int dtype, long long ldx, int C, int K,
                                        const void* __restrict__ taps, int taps_dtype, const float* __restrict__ state,
                                        const int* __restrict__ seq_of, const int* __restrict__ cu,
-                                       const int* __restrict__ slots, void* __restrict__ out, long long ldo) {
+                                       const int* __restrict__ slots, void* __restrict__ out, long long ldo,
+                                       const void* __restrict__ bias, int act) {
     const int t = blockIdx.x;
     const int b = seq_of[t];
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -35,7 +36,8 @@ __global__ void short_conv_silu_kernel(const void* __restrict__ xin, int dtype, 
                                       : st[size_t(K - 1 + src) * C + c];
             acc = fmaf(xv, gb_load(taps, taps_dtype, size_t(c) * K + j), acc);
         }
-        gb_store(out, dtype, size_t(t) * ldo + c, acc / (1.f + expf(-acc)));
+        if (bias) acc += gb_load(bias, taps_dtype, c);
+        gb_store(out, dtype, size_t(t) * ldo + c, act ? acc / (1.f + expf(-acc)) : acc);
     }
 }
 
@@ -54,7 +56,8 @@ __device__ __forceinline__ void conv_unpack8(uint4 raw, float* f) {
 __global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(
         const __nv_bfloat16* __restrict__ xin, long long ldx, int C, int K, const __nv_bfloat16* __restrict__ taps_t,
         const float* __restrict__ state, const int* __restrict__ seq_of, const int* __restrict__ cu,
-        const int* __restrict__ slots, __nv_bfloat16* __restrict__ out, long long ldo) {
+        const int* __restrict__ slots, __nv_bfloat16* __restrict__ out, long long ldo, const __nv_bfloat16* __restrict__ bias,
+        int act) {
     const int t = blockIdx.x;
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     if (c >= C) return;
@@ -83,11 +86,20 @@ __global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = fmaf(xv[e], tw[e], acc[e]);
     }
+    if (bias) {
+        float bv[8];
+        conv_unpack8(*reinterpret_cast<const uint4*>(bias + c), bv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bv[e];
+    }
+    if (act) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.f + expf(-acc[e]));
+    }
     uint4 packed;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-        o2[e] = __floats2bfloat162_rn(acc[2 * e] / (1.f + expf(-acc[2 * e])), acc[2 * e + 1] / (1.f + expf(-acc[2 * e + 1])));
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
     *dst = packed;
 }
 
@@ -123,30 +135,43 @@ __global__ void short_conv_carry_kernel(const void* __restrict__ xin, int dtype,
 // xin: [T, C] with pitch ldx (the projections' outputs); taps [C, K], last column on the current token;
 // state f32 [slots, K-1, C]; out [T, C] with pitch ldo, same dtype as xin.  The carried inputs are renewed.
 // taps_t (optional): the taps again as bfloat16 [K, C], for the kernel of 16-byte accesses.
+// bias [C] (optional, of the taps' dtype) is added to the sum; act 1: SiLU follows, 0: nothing does.
+GB_API int gb_short_conv(const void* xin, int dtype, long long ldx, int T, int B, int C, int K, const void* taps,
+                         int taps_dtype, const void* taps_t, const void* bias, int act, float* state, const int* seq_of,
+                         const int* cu, const int* slots, const int* qlens, void* out, long long ldo, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(taps_dtype), "gb_short_conv: bad dtype");
+    GB_REQUIRE(C > 0 && K >= 1 && K <= CONV_MAX_TAPS && ldx >= C && ldo >= C, "gb_short_conv: bad sizes C=%d taps=%d (1..%d)",
+               C, K, CONV_MAX_TAPS);
+    GB_REQUIRE(K == 1 || state, "gb_short_conv: a convolution of %d taps needs the carried inputs", K);
+    GB_REQUIRE(act == 0 || act == 1, "gb_short_conv: unknown activation %d", act);
+    if (T == 0) return 0;
+    const int threads = 128, slices = (C + threads - 1) / threads;
+    GB_REQUIRE(slices <= 65535, "gb_short_conv: too many channels (%d)", C);
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    if (taps_t && dtype == GB_BF16 && C % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0 && aligned16(xin) && aligned16(out) &&
+        aligned16(taps_t) && (K == 1 || (reinterpret_cast<uintptr_t>(state) & 31) == 0) &&
+        (!bias || (taps_dtype == GB_BF16 && aligned16(bias)))) {
+        short_conv_silu_vec_kernel<<<dim3(T, (C / 8 + threads - 1) / threads), threads, 0, stream>>>(
+            (const __nv_bfloat16*)xin, ldx, C, K, (const __nv_bfloat16*)taps_t, state, seq_of, cu, slots, (__nv_bfloat16*)out, ldo,
+            (const __nv_bfloat16*)bias, act);
+    } else {
+        short_conv_silu_kernel<<<dim3(T, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu,
+                                                                       slots, out, ldo, bias, act);
+    }
+    GB_LAUNCH_OK("gb_short_conv");
+    if (K > 1 && B > 0) {
+        short_conv_carry_kernel<<<dim3(B, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, state, cu, slots, qlens);
+        GB_LAUNCH_OK("gb_short_conv (carry)");
+    }
+    return 0;
+}
+
+// The convolution followed by SiLU, without a bias.
 GB_API int gb_short_conv_silu(const void* xin, int dtype, long long ldx, int T, int B, int C, int K, const void* taps,
                               int taps_dtype, const void* taps_t, float* state, const int* seq_of, const int* cu,
                               const int* slots, const int* qlens, void* out, long long ldo, cudaStream_t stream) {
-    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(taps_dtype), "gb_short_conv_silu: bad dtype");
-    GB_REQUIRE(C > 0 && K >= 1 && K <= CONV_MAX_TAPS && ldx >= C && ldo >= C, "gb_short_conv_silu: bad sizes C=%d taps=%d (1..%d)",
-               C, K, CONV_MAX_TAPS);
-    GB_REQUIRE(K == 1 || state, "gb_short_conv_silu: a convolution of %d taps needs the carried inputs", K);
-    if (T == 0) return 0;
-    const int threads = 128, slices = (C + threads - 1) / threads;
-    GB_REQUIRE(slices <= 65535, "gb_short_conv_silu: too many channels (%d)", C);
-    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
-    if (taps_t && dtype == GB_BF16 && C % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0 && aligned16(xin) && aligned16(out) &&
-        aligned16(taps_t) && (K == 1 || (reinterpret_cast<uintptr_t>(state) & 31) == 0)) {
-        short_conv_silu_vec_kernel<<<dim3(T, (C / 8 + threads - 1) / threads), threads, 0, stream>>>(
-            (const __nv_bfloat16*)xin, ldx, C, K, (const __nv_bfloat16*)taps_t, state, seq_of, cu, slots, (__nv_bfloat16*)out, ldo);
-    } else {
-        short_conv_silu_kernel<<<dim3(T, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu, slots, out, ldo);
-    }
-    GB_LAUNCH_OK("gb_short_conv_silu");
-    if (K > 1 && B > 0) {
-        short_conv_carry_kernel<<<dim3(B, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, state, cu, slots, qlens);
-        GB_LAUNCH_OK("gb_short_conv_silu (carry)");
-    }
-    return 0;
+    return gb_short_conv(xin, dtype, ldx, T, B, C, K, taps, taps_dtype, taps_t, nullptr, 1, state, seq_of, cu, slots, qlens, out,
+                         ldo, stream);
 }
 
 // ------------------------------------------------------------ the recurrence
@@ -398,37 +423,54 @@ GB_API int gb_delta_rule(const void* q, const void* k, const void* v, int dtype,
 
 // --------------------------------------------- per-head RMS norm, weight, gate
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[:] * f(gate[t, h, :]); one warp per
-// (token, head); w [Dv] is shared by the heads.  f: 0 the sigmoid, 1 SiLU (z sigmoid(z)).
+// (token, head); w [Dv] is shared by the heads, or every head has its own (w_per_head: w [H, Dv]).
+// f: 0 the sigmoid, 1 SiLU (z sigmoid(z)).  gate_first: the gate comes before the norm,
+// out = y / sqrt(mean(y^2) + eps) * w with y = o f(gate).
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ gate,
                                        int gate_dtype, long long ldg, const void* __restrict__ w, int w_dtype, float eps,
                                        void* __restrict__ out, int out_dtype, long long ld_out, long long items, int H, int Dv,
-                                       int gate_act) {
+                                       int gate_act, int w_per_head, int gate_first) {
     const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= items) return;
     const int lane = threadIdx.x & 31;
     const long long t = item / H;
     const int h = int(item - t * H);
     const float* orow = o + t * ldo + size_t(h) * Dv;
+    const size_t wrow = w_per_head ? size_t(h) * Dv : 0;
     float ss = 0.f;
+    if (gate_first) {
+        for (int d = lane; d < Dv; d += 32) {
+            const float gt = gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * Dv + d);
+            const float y = orow[d] * ((gate_act ? gt : 1.f) / (1.f + expf(-gt)));
+            ss = fmaf(y, y, ss);
+        }
+        const float rms = sqrtf(gb_warp_sum(ss) / float(Dv) + eps);
+        for (int d = lane; d < Dv; d += 32) {
+            const float gt = gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * Dv + d);
+            const float y = orow[d] * ((gate_act ? gt : 1.f) / (1.f + expf(-gt)));
+            gb_store(out, out_dtype, size_t(t) * ld_out + size_t(h) * Dv + d, y / rms * gb_load(w, w_dtype, wrow + d));
+        }
+        return;
+    }
     for (int d = lane; d < Dv; d += 32) ss = fmaf(orow[d], orow[d], ss);
     const float rms = sqrtf(gb_warp_sum(ss) / float(Dv) + eps);
     for (int d = lane; d < Dv; d += 32) {
         const float gt = gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * Dv + d);
         gb_store(out, out_dtype, size_t(t) * ld_out + size_t(h) * Dv + d,
-                 orow[d] / rms * gb_load(w, w_dtype, d) * ((gate_act ? gt : 1.f) / (1.f + expf(-gt))));
+                 orow[d] / rms * gb_load(w, w_dtype, wrow + d) * ((gate_act ? gt : 1.f) / (1.f + expf(-gt))));
     }
 }
 
 GB_API int gb_gated_head_norm(const float* o, long long ldo, const void* gate, int gate_dtype, long long ldg, const void* w,
                               int w_dtype, float eps, void* out, int out_dtype, long long ld_out, int T, int H, int Dv,
-                              int gate_act, cudaStream_t stream) {
+                              int gate_act, int w_per_head, int gate_first, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(gate_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(out_dtype), "gb_gated_head_norm: bad dtype");
     GB_REQUIRE(H > 0 && Dv > 0 && eps > 0.f, "gb_gated_head_norm: bad sizes heads=%d vdim=%d eps=%g", H, Dv, eps);
     GB_REQUIRE(gate_act == 0 || gate_act == 1, "gb_gated_head_norm: unknown gate function %d", gate_act);
     if (T == 0) return 0;
     const long long items = (long long)T * H;
     gated_head_norm_kernel<<<unsigned((items + 3) / 4), 128, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out,
-                                                                          out_dtype, ld_out, items, H, Dv, gate_act);
+                                                                          out_dtype, ld_out, items, H, Dv, gate_act, w_per_head, gate_first);
     GB_LAUNCH_OK("gb_gated_head_norm");
     return 0;
 }

@@ -11,9 +11,13 @@
 // once at the start and written once at the end.  A sequence that brings many tokens is cut into segments that are walked
 // side by side: every segment from a zero state, then the states at the segments' starts by a short carry
 // (S <- diag(product of the segment's decays) S + the segment's own state), then every segment again from its start.
+// The walk serves every mixer whose state obeys S <- diag(decay) S + k v^T: its two options are reading the state before
+// the token's own update instead of after it, and a number per (token, head) times the token's value added to what is read
+// (a bonus for the current token, or a skip path); a mixer brings its own preparation kernel (linear_walk.h).
 #include <math.h>
 
 #include "common.cuh"
+#include "linear_walk.h"
 
 struct GlaPrepParams {
     const void *q, *k, *v;          // q, k [T, H*D], v [T, H*Dv]: column slices of one buffer, rows `ld` apart
@@ -63,6 +67,7 @@ struct GlaWalkParams {
     // state at its start), read out, no state written.
     int mode, seg_len, n_seg;
     float* seg_state;
+    const float* bonus;             // [T, H, 4] (first entry counts) or null: out += bonus * v
 };
 
 __device__ __forceinline__ void gla_cp16(float* dst, const float* src) {
@@ -70,7 +75,8 @@ __device__ __forceinline__ void gla_cp16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int NR>
+// BEFORE: what a token reads is the state as the token before it left it (its own k v^T is not in it).
+template <int NR, bool BEFORE>
 __global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
     extern __shared__ __align__(16) float gla_sm[];
     float* sm = gla_sm;
@@ -80,7 +86,7 @@ __global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
     if (slot < 0 || n <= 0) return;
     const int R = p.R, CW = 32 / R, CB = 4 * CW, D = p.D, Dv = p.Dv, DA = p.DA, TC = p.TC;
     const int RS = R * (NR + 4);                        // floats of one padded row of q, k or decays
-    const int TOK = 3 * RS + CB;                        // floats per token: q, k, decays, values of the slice
+    const int TOK = 3 * RS + CB + 4;                    // floats per token: q, k, decays, values of the slice, bonus
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane / CW, jj = lane - r * CW;
     const int col0 = blockIdx.z * CB;
@@ -101,12 +107,14 @@ __global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
     auto load_chunk = [&](int c0, int buf) {
         const int nt = min(TC, n - c0);
         float* base = sm + buf * TC * TOK;
-        const int per = 3 * q4 + v4;
+        const int per = 3 * q4 + v4 + (p.bonus ? 1 : 0);
         for (int idx = threadIdx.x; idx < nt * per; idx += 128) {
             const int tt = idx / per, e = idx - tt * per;
             const size_t t = size_t(t0 + c0 + tt);
             float* row = base + tt * TOK;
-            if (e < 3 * q4) {
+            if (e == 3 * q4 + v4) {
+                gla_cp16(row + 3 * RS + CB, p.bonus + (t * p.H + h) * 4);
+            } else if (e < 3 * q4) {
                 const int which = e / q4, k4 = e - which * q4, i = 4 * k4;
                 gla_cp16(row + which * RS + (i / NR) * (NR + 4) + (i % NR), p.qkg + ((t * p.H + h) * 3 + which) * DA + i);
             } else {
@@ -135,13 +143,21 @@ __global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
 #pragma unroll
             for (int m = 0; m < NR / 4; ++m) {
                 const float4 gv = gg[m], kv = kk[m], qv = qq[m];
-                S[4 * m] = fmaf(kv.x, vj, S[4 * m] * gv.x);         o0 = fmaf(S[4 * m], qv.x, o0);
-                S[4 * m + 1] = fmaf(kv.y, vj, S[4 * m + 1] * gv.y); o1 = fmaf(S[4 * m + 1], qv.y, o1);
-                S[4 * m + 2] = fmaf(kv.z, vj, S[4 * m + 2] * gv.z); o2 = fmaf(S[4 * m + 2], qv.z, o2);
-                S[4 * m + 3] = fmaf(kv.w, vj, S[4 * m + 3] * gv.w); o3 = fmaf(S[4 * m + 3], qv.w, o3);
+                if (BEFORE) {
+                    o0 = fmaf(S[4 * m], qv.x, o0);     S[4 * m] = fmaf(kv.x, vj, S[4 * m] * gv.x);
+                    o1 = fmaf(S[4 * m + 1], qv.y, o1); S[4 * m + 1] = fmaf(kv.y, vj, S[4 * m + 1] * gv.y);
+                    o2 = fmaf(S[4 * m + 2], qv.z, o2); S[4 * m + 2] = fmaf(kv.z, vj, S[4 * m + 2] * gv.z);
+                    o3 = fmaf(S[4 * m + 3], qv.w, o3); S[4 * m + 3] = fmaf(kv.w, vj, S[4 * m + 3] * gv.w);
+                } else {
+                    S[4 * m] = fmaf(kv.x, vj, S[4 * m] * gv.x);         o0 = fmaf(S[4 * m], qv.x, o0);
+                    S[4 * m + 1] = fmaf(kv.y, vj, S[4 * m + 1] * gv.y); o1 = fmaf(S[4 * m + 1], qv.y, o1);
+                    S[4 * m + 2] = fmaf(kv.z, vj, S[4 * m + 2] * gv.z); o2 = fmaf(S[4 * m + 2], qv.z, o2);
+                    S[4 * m + 3] = fmaf(kv.w, vj, S[4 * m + 3] * gv.w); o3 = fmaf(S[4 * m + 3], qv.w, o3);
+                }
             }
             float o = (o0 + o1) + (o2 + o3);
             for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (p.bonus) o = fmaf(row[3 * RS + CB], vj, o);
             if (r == 0 && col_ok && p.mode != 1) p.out[size_t(t0 + c0 + tt) * p.ldo + size_t(h) * Dv + j] = o;
         }
         __syncthreads();                                   // this buffer is loaded again two chunks on
@@ -208,6 +224,11 @@ GB_API long long gb_gla_scratch_floats(int T, int H, int D, int Dv) {
     return (long long)T * H * (3 * DA + VA);
 }
 
+// The same with room for a number per (token, head) behind the rows (four floats each).
+GB_API long long gb_linear_walk_scratch_floats(int T, int H, int D, int Dv) {
+    return gb_gla_scratch_floats(T, H, D, Dv) + (long long)T * H * 4;
+}
+
 // Sequences of more than GLA_SEG_FROM new tokens are walked in segments of GLA_SEG side by side: twice the arithmetic of one
 // walk, on as many blocks as there are segments (a prompt of 2,048 tokens, 16 heads of 128 x 128: 1.02 ms as one walk).
 constexpr int GLA_SEG = 128, GLA_SEG_FROM = 256;
@@ -218,6 +239,82 @@ GB_API long long gb_gla_segment_floats(int B, int max_qlen, int H, int D, int Dv
     if (max_qlen <= GLA_SEG_FROM) return 0;
     const long long n_seg = (max_qlen + GLA_SEG - 1) / GLA_SEG, DA = (D + 3) / 4 * 4;
     return (long long)B * n_seg * H * ((long long)D * Dv + DA);
+}
+
+LinearWalkRows gb_linear_walk_rows(float* scratch, int T, int H, int D, int Dv, bool with_bonus) {
+    LinearWalkRows r;
+    r.DA = (D + 3) / 4 * 4;
+    r.VA = (Dv + 3) / 4 * 4;
+    r.qkg = scratch;
+    r.vf = scratch + size_t(T) * H * 3 * r.DA;
+    r.bonus = with_bonus ? r.vf + size_t(T) * H * r.VA : nullptr;
+    return r;
+}
+
+int gb_linear_walk_launch(const LinearWalkRows& rows, bool before, float* state, float* out, long long ldo, const int* cu,
+                          const int* slots, const int* qlens, int B, int H, int D, int Dv, int max_qlen, float* seg_scratch,
+                          cudaStream_t stream, const char* who) {
+    GB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 2048, "%s: bad sizes heads=%d dim=%d vdim=%d (dim up to 2048)", who, H, D, Dv);
+    GB_REQUIRE(rows.qkg && (reinterpret_cast<uintptr_t>(rows.qkg) & 15) == 0, "%s: scratch missing or misaligned", who);
+    const int DA = rows.DA, VA = rows.VA;
+    GlaWalkParams p;
+    p.qkg = rows.qkg; p.vf = rows.vf; p.bonus = rows.bonus; p.state = state; p.out = out; p.cu = cu; p.slots = slots; p.qlens = qlens;
+    p.ldo = ldo; p.H = H; p.D = D; p.Dv = Dv; p.DA = DA; p.VA = VA;
+    int NR, R;
+    gla_shape(D, &NR, &R);
+    const int CB = 4 * (32 / R);
+    const int per_token = 4 * (3 * R * (NR + 4) + CB + 4);
+    int TC = (20 * 1024) / per_token;                    // two buffers of at most 20 KB each
+    TC = TC < 1 ? 1 : (TC > 16 ? 16 : TC);
+    p.R = R; p.TC = TC;
+    const size_t smem = size_t(2) * TC * per_token;
+    GB_REQUIRE(smem <= 64 * 1024, "%s: key size %d needs %zu bytes of shared memory", who, D, smem);
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(gla_walk_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess ||
+                cudaFuncSetAttribute(gla_walk_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+                return gb_fail("%s: cannot get %zu bytes of shared memory", who, smem);
+            configured = true;
+        }
+    }
+    dim3 grid(B, H, (Dv + CB - 1) / CB);
+    GB_REQUIRE(grid.z <= 65535 && H <= 65535, "%s: too many heads or value columns", who);
+    auto walk = [&](const GlaWalkParams& w, dim3 g) {
+        if (before) {
+            if (NR == 8) gla_walk_kernel<8, true><<<g, 128, smem, stream>>>(w);
+            else if (NR == 16) gla_walk_kernel<16, true><<<g, 128, smem, stream>>>(w);
+            else if (NR == 32) gla_walk_kernel<32, true><<<g, 128, smem, stream>>>(w);
+            else gla_walk_kernel<64, true><<<g, 128, smem, stream>>>(w);
+        } else {
+            if (NR == 8) gla_walk_kernel<8, false><<<g, 128, smem, stream>>>(w);
+            else if (NR == 16) gla_walk_kernel<16, false><<<g, 128, smem, stream>>>(w);
+            else if (NR == 32) gla_walk_kernel<32, false><<<g, 128, smem, stream>>>(w);
+            else gla_walk_kernel<64, false><<<g, 128, smem, stream>>>(w);
+        }
+    };
+    p.mode = 0; p.seg_len = 0; p.n_seg = 1; p.seg_state = nullptr;
+    if (max_qlen <= GLA_SEG_FROM || !seg_scratch) {
+        walk(p, grid);
+        GB_LAUNCH_OK(who);
+        return 0;
+    }
+    const int n_seg = (max_qlen + GLA_SEG - 1) / GLA_SEG;
+    float* prod = seg_scratch + size_t(B) * n_seg * H * size_t(D) * Dv;
+    p.seg_len = GLA_SEG; p.n_seg = n_seg; p.seg_state = seg_scratch;
+    dim3 seg_grid(B * n_seg, H, grid.z);
+    p.mode = 1;
+    walk(p, seg_grid);
+    GB_LAUNCH_OK(who);
+    gla_decay_prod_kernel<<<dim3(B * n_seg, H), 128, 0, stream>>>(p.qkg, cu, qlens, H, DA, GLA_SEG, n_seg, prod);
+    GB_LAUNCH_OK(who);
+    GB_REQUIRE((D * Dv + 255) / 256 <= 65535, "%s: state too large", who);
+    gla_carry_kernel<<<dim3(B, H, (D * Dv + 255) / 256), 256, 0, stream>>>(state, seg_scratch, prod, slots, qlens, H, D, Dv, DA, GLA_SEG, n_seg);
+    GB_LAUNCH_OK(who);
+    p.mode = 2;
+    walk(p, seg_grid);
+    GB_LAUNCH_OK(who);
+    return 0;
 }
 
 // q, k [T, H*D] and v [T, H*Dv]: column slices of one buffer with rows ld apart; a [T, H*D] the decay's
@@ -231,62 +328,13 @@ GB_API int gb_gla(const void* q, const void* k, const void* v, int dtype, long l
     GB_REQUIRE(inv_tau > 0.f, "gb_gla: the decay's exponent must be positive");
     GB_REQUIRE(scratch && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0, "gb_gla: scratch missing or misaligned");
     if (B == 0 || T == 0) return 0;
-    const int DA = (D + 3) / 4 * 4, VA = (Dv + 3) / 4 * 4;
+    const LinearWalkRows rows = gb_linear_walk_rows(scratch, T, H, D, Dv, false);
     GlaPrepParams pp;
-    pp.q = q; pp.k = k; pp.v = v; pp.a = a; pp.bias = bias; pp.qkg = scratch; pp.vf = scratch + size_t(T) * H * 3 * DA;
+    pp.q = q; pp.k = k; pp.v = v; pp.a = a; pp.bias = bias; pp.qkg = rows.qkg; pp.vf = rows.vf;
     pp.ld = ld; pp.ld_a = ld_a; pp.dtype = dtype; pp.a_dtype = a_dtype; pp.w_dtype = w_dtype; pp.H = H; pp.D = D; pp.Dv = Dv;
-    pp.DA = DA; pp.VA = VA; pp.q_scale = q_scale; pp.inv_tau = inv_tau;
+    pp.DA = rows.DA; pp.VA = rows.VA; pp.q_scale = q_scale; pp.inv_tau = inv_tau;
     GB_REQUIRE((H + 3) / 4 <= 65535, "gb_gla: too many heads (%d)", H);
     gla_prep_kernel<<<dim3(T, (H + 3) / 4), 128, 0, stream>>>(pp);
     GB_LAUNCH_OK("gb_gla (prepare)");
-    GlaWalkParams p;
-    p.qkg = pp.qkg; p.vf = pp.vf; p.state = state; p.out = out; p.cu = cu; p.slots = slots; p.qlens = qlens;
-    p.ldo = ldo; p.H = H; p.D = D; p.Dv = Dv; p.DA = DA; p.VA = VA;
-    int NR, R;
-    gla_shape(D, &NR, &R);
-    const int CB = 4 * (32 / R);
-    const int per_token = 4 * (3 * R * (NR + 4) + CB);
-    int TC = (20 * 1024) / per_token;                    // two buffers of at most 20 KB each
-    TC = TC < 1 ? 1 : (TC > 16 ? 16 : TC);
-    p.R = R; p.TC = TC;
-    const size_t smem = size_t(2) * TC * per_token;
-    GB_REQUIRE(smem <= 64 * 1024, "gb_gla: key size %d needs %zu bytes of shared memory", D, smem);
-    if (smem > 48 * 1024) {
-        static bool configured = false;
-        if (!configured) {
-            if (cudaFuncSetAttribute(gla_walk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
-                return gb_fail("gb_gla: cannot get %zu bytes of shared memory", smem);
-            configured = true;
-        }
-    }
-    dim3 grid(B, H, (Dv + CB - 1) / CB);
-    GB_REQUIRE(grid.z <= 65535 && H <= 65535, "gb_gla: too many heads or value columns");
-    auto walk = [&](const GlaWalkParams& w, dim3 g) {
-        if (NR == 8) gla_walk_kernel<8><<<g, 128, smem, stream>>>(w);
-        else if (NR == 16) gla_walk_kernel<16><<<g, 128, smem, stream>>>(w);
-        else if (NR == 32) gla_walk_kernel<32><<<g, 128, smem, stream>>>(w);
-        else gla_walk_kernel<64><<<g, 128, smem, stream>>>(w);
-    };
-    p.mode = 0; p.seg_len = 0; p.n_seg = 1; p.seg_state = nullptr;
-    if (max_qlen <= GLA_SEG_FROM || !seg_scratch) {
-        walk(p, grid);
-        GB_LAUNCH_OK("gb_gla");
-        return 0;
-    }
-    const int n_seg = (max_qlen + GLA_SEG - 1) / GLA_SEG;
-    float* prod = seg_scratch + size_t(B) * n_seg * H * size_t(D) * Dv;
-    p.seg_len = GLA_SEG; p.n_seg = n_seg; p.seg_state = seg_scratch;
-    dim3 seg_grid(B * n_seg, H, grid.z);
-    p.mode = 1;
-    walk(p, seg_grid);
-    GB_LAUNCH_OK("gb_gla (segments from zero)");
-    gla_decay_prod_kernel<<<dim3(B * n_seg, H), 128, 0, stream>>>(p.qkg, cu, qlens, H, DA, GLA_SEG, n_seg, prod);
-    GB_LAUNCH_OK("gb_gla (decay products)");
-    GB_REQUIRE((D * Dv + 255) / 256 <= 65535, "gb_gla: state too large");
-    gla_carry_kernel<<<dim3(B, H, (D * Dv + 255) / 256), 256, 0, stream>>>(state, seg_scratch, prod, slots, qlens, H, D, Dv, DA, GLA_SEG, n_seg);
-    GB_LAUNCH_OK("gb_gla (carry)");
-    p.mode = 2;
-    walk(p, seg_grid);
-    GB_LAUNCH_OK("gb_gla (segments)");
-    return 0;
+    return gb_linear_walk_launch(rows, false, state, out, ldo, cu, slots, qlens, B, H, D, Dv, max_qlen, seg_scratch, stream, "gb_gla");
 }

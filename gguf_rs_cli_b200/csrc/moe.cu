@@ -303,7 +303,7 @@ __global__ void unary_act_kernel(void* __restrict__ x, int dtype, long long n, i
 
 // x <- act(x) entry by entry, in place (contiguous).  act: GbGateAct or GbUnaryAct.
 GB_API int gb_unary_act(void* x, int dtype, long long n, int act, cudaStream_t stream) {
-    GB_REQUIRE(gb_is_dtype(dtype) && act >= 1 && act <= 3, "gb_unary_act: bad dtype or activation %d", act);
+    GB_REQUIRE(gb_is_dtype(dtype) && act >= 1 && act <= 4, "gb_unary_act: bad dtype or activation %d", act);
     if (n == 0) return 0;
     unary_act_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(x, dtype, n, act);
     GB_LAUNCH_OK("gb_unary_act");

@@ -52,3 +52,17 @@ GB_API int gb_scale(float* x, long long n, float scale, cudaStream_t stream) {
     GB_LAUNCH_OK("gb_scale");
     return 0;
 }
+
+// x[i] <- cap tanh(x[i] / cap) for n 32-bit values (logits that a model bounds softly).
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) x[i] = cap * tanhf(x[i] / cap);
+}
+
+GB_API int gb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && cap > 0.f, "gb_softcap: bad size %lld or cap %g", n, cap);
+    if (n == 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    softcap_kernel<<<int(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(x, size_t(n), cap);
+    GB_LAUNCH_OK("gb_softcap");
+    return 0;
+}

@@ -79,15 +79,16 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
                       seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                       kcache: torch.Tensor, vcache: Optional[torch.Tensor], window: int, scale: float,
                       v_dim: Optional[int] = None, keep_first: int = 0, head_pages: int = 0,
-                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
     """v_dim: entries of a value when they differ from a key's head_dim.  vcache None: the values are the
     first v_dim entries of the key rows themselves (one latent row per position serves as key and value).
     keep_first: with a window, the sequence's first positions that stay visible behind it; their pages are the first
     head_pages entries of the page table, in front of the ring.  gate [T, heads*v_dim]: the result is multiplied by
-    sigmoid(gate)."""
+    sigmoid(gate); a gate [T, heads] holds one number per head.  sink: the softmax's denominator counts one more key
+    of score 0 that has no value."""
     _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
-    assert gate is None or (gate.stride(1) == 1 and gate.shape == out.shape)
     T = q.shape[0]
+    per_head = _gate_per_head(gate, out, n_heads)
     v_dim = head_dim if v_dim is None else int(v_dim)
     v_row = head_dim if vcache is None else vcache.shape[-1]
     assert kcache.shape[-1] == head_dim and v_row >= v_dim and (vcache is None or vcache.dtype == kcache.dtype)
@@ -96,8 +97,19 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
          n_heads, n_kv_heads, head_dim, v_dim, v_row, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages,
          ptr(kcache), ptr(kcache if vcache is None else vcache), dtype_code(kcache), int(window or 0), float(scale),
          int(head_pages), int(keep_first or 0), ptr(gate), 0 if gate is None else dtype_code(gate),
-         0 if gate is None else gate.stride(0), stream_ptr())
+         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
     return out
+
+
+def _gate_per_head(gate: Optional[torch.Tensor], out: torch.Tensor, n_heads: int) -> bool:
+    """Whether a gate holds one number per head ([T, heads]) instead of one per entry of the result."""
+    if gate is None:
+        return False
+    assert gate.stride(1) == 1 and gate.shape[0] == out.shape[0]
+    if gate.shape[1] == n_heads and out.shape[1] != n_heads:
+        return True
+    assert gate.shape == out.shape
+    return False
 
 
 GATE_ACTS = {"silu": 1, "gelu_tanh": 2}
@@ -158,6 +170,137 @@ def short_conv_silu(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch
     return out
 
 
+def short_conv(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], ctx, out: torch.Tensor,
+               taps_t: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> torch.Tensor:
+    """short_conv_silu with its options open: bias [C] (of the taps' dtype) is added to the sum, activation None or "silu"."""
+    _cuda(xin, taps, state, out, taps_t, bias)
+    assert taps_t is None or (taps_t.dtype == torch.bfloat16 and taps_t.shape == (taps.shape[1], taps.shape[0]) and taps_t.is_contiguous())
+    assert activation in (None, "silu")
+    T, C = xin.shape
+    K = taps.shape[1]
+    assert taps.shape == (C, K) and taps.is_contiguous() and xin.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape == (T, C) and out.dtype == xin.dtype
+    assert bias is None or (bias.shape == (C,) and bias.dtype == taps.dtype and bias.is_contiguous())
+    assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (K - 1, C) and state.is_contiguous())
+    call("gb_short_conv", ptr(xin), dtype_code(xin), xin.stride(0), T, ctx.B, C, K, ptr(taps), dtype_code(taps), ptr(taps_t),
+         ptr(bias), 1 if activation else 0, ptr(state), ptr(ctx.seq_of), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out),
+         out.stride(0), stream_ptr())
+    return out
+
+
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, carried: torch.Tensor, ctx, out: torch.Tensor) -> torch.Tensor:
+    """out[s, t, :] = h[t] + (h[t-1] - h[t]) * mu[s] for every blend s; the row before a sequence's first token of the
+    step is carried [slots, E] (float32; zero when the sequence starts), which then receives the step's last row."""
+    _cuda(h, mu, carried, out)
+    T, E = h.shape
+    S = mu.shape[0]
+    assert h.stride(1) == 1 and mu.shape == (S, E) and mu.is_contiguous() and out.shape == (S, T, E) and out.is_contiguous()
+    assert out.dtype == h.dtype and carried.dtype == torch.float32 and carried.shape[1:] == (E,) and carried.is_contiguous()
+    call("gb_token_shift_mix", ptr(h), dtype_code(h), h.stride(0), T, E, ptr(mu), dtype_code(mu), S, ptr(carried), ptr(ctx.seq_of),
+         ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), stream_ptr())
+    return out
+
+
+def _walk_scratch(ctx, n_heads: int, dim: int, vdim: int):
+    """Workspace of the walk over tokens that the mixers with a matrix state share: prepared rows, and room for the
+    segments of long sequences."""
+    lib = native.library()
+    scratch = ctx.ws.get("walk.prepared", (lib.gb_linear_walk_scratch_floats(ctx.T, n_heads, dim, vdim),), torch.float32)
+    seg = lib.gb_gla_segment_floats(ctx.B, ctx.max_qlen, n_heads, dim, vdim)
+    return scratch, (ctx.ws.get("walk.segments", (seg,), torch.float32) if seg else None)
+
+
+def wkv(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, w0: torch.Tensor, u: torch.Tensor,
+        state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int, dim: int) -> torch.Tensor:
+    """Per head, from and into state [slots, heads, dim, dim] (float32): out = (S + diag(u) k v^T)^T r, then
+    S <- diag(w) S + k v^T with w = exp(-exp(a + w0)) per key channel.  r, k, v [T, heads*dim]; a [T, heads*dim] the
+    decay's low-rank result; out float32 [T, heads*dim]."""
+    _cuda(r, k, v, a, w0, u, state, out)
+    T = r.shape[0]
+    for t in (r, k, v, a):
+        assert t.stride(1) == 1 and t.shape == (T, n_heads * dim)
+    assert r.dtype == k.dtype == v.dtype and w0.dtype == u.dtype and w0.numel() == u.numel() == n_heads * dim
+    assert w0.is_contiguous() and u.is_contiguous()
+    assert state.dtype == torch.float32 and state.shape[1:] == (n_heads, dim, dim) and state.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, n_heads * dim) and out.stride(1) == 1
+    scratch, seg = _walk_scratch(ctx, n_heads, dim, dim)
+    call("gb_wkv", ptr(r), r.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), dtype_code(r), ptr(a), dtype_code(a), a.stride(0),
+         ptr(w0), ptr(u), dtype_code(w0), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens),
+         T, ctx.B, n_heads, dim, ptr(scratch), int(ctx.max_qlen), ptr(seg), stream_ptr())
+    if seg is not None:
+        native.count_launches(3)
+    return out
+
+
+def ssd(x: torch.Tensor, bm: torch.Tensor, cm: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+        skip: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int, n_groups: int, n_state: int,
+        vdim: int) -> torch.Tensor:
+    """The selective state-space recurrence per head, from and into state [slots, heads, n_state, vdim] (float32):
+    dt' = softplus(dt + dt_bias); S <- exp(-exp(a_log) dt') S + dt' B x^T; out = S^T C + skip x.  x [T, heads*vdim],
+    bm, cm [T, groups*n_state]: column slices of one buffer; dt [T, heads]; out float32 [T, heads*vdim]."""
+    _cuda(x, bm, cm, dt, dt_bias, a_log, skip, state, out)
+    T, ld = x.shape[0], x.stride(0)
+    assert bm.stride(0) == ld and cm.stride(0) == ld and x.dtype == bm.dtype == cm.dtype
+    assert x.stride(1) == 1 and bm.stride(1) == 1 and cm.stride(1) == 1 and dt.stride(1) == 1
+    assert x.shape == (T, n_heads * vdim) and bm.shape == cm.shape == (T, n_groups * n_state) and dt.shape == (T, n_heads)
+    assert dt_bias.dtype == a_log.dtype == skip.dtype and dt_bias.numel() == a_log.numel() == skip.numel() == n_heads
+    assert state.dtype == torch.float32 and state.shape[1:] == (n_heads, n_state, vdim) and state.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, n_heads * vdim) and out.stride(1) == 1
+    scratch, seg = _walk_scratch(ctx, n_heads, n_state, vdim)
+    call("gb_ssd", ptr(x), ptr(bm), ptr(cm), dtype_code(x), ld, ptr(dt), dtype_code(dt), dt.stride(0), ptr(dt_bias), ptr(a_log),
+         ptr(skip), dtype_code(dt_bias), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens),
+         T, ctx.B, n_heads, n_groups, n_state, vdim, ptr(scratch), int(ctx.max_qlen), ptr(seg), stream_ptr())
+    if seg is not None:
+        native.count_launches(3)
+    return out
+
+
+def add_rmsnorm_pair(x: torch.Tensor, terms, weight: torch.Tensor, weight2: Optional[torch.Tensor], offset: float, eps: float,
+                     out: torch.Tensor, out2: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                     write_x: bool = True) -> None:
+    """x float32 [T,E] += the sum of up to three terms [T,E]; out = x / sqrt(mean(x^2) + eps) * (offset + weight), and
+    out2 the same with weight2 when given.  rows: int32 row numbers to gather (then the results have len(rows) rows)."""
+    _cuda(x, weight, weight2, out, out2, rows, *terms)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and weight.numel() == E and len(terms) <= 3
+    assert (weight2 is None) == (out2 is None) and (weight2 is None or (weight2.dtype == weight.dtype and weight2.numel() == E))
+    n_rows = T if rows is None else rows.numel()
+    assert out.shape == (n_rows, E) and (out2 is None or (out2.shape == out.shape and out2.dtype == out.dtype and out2.is_contiguous()))
+    args = []
+    for i in range(3):
+        t = terms[i] if i < len(terms) else None
+        assert t is None or (t.shape == (T, E) and t.is_contiguous())
+        args += [ptr(t), 0 if t is None else dtype_code(t)]
+    call("gb_add_rmsnorm_pair", ptr(x), *args, len(terms), ptr(rows), n_rows, E, ptr(weight), ptr(weight2), dtype_code(weight),
+         float(offset), float(eps), ptr(out), ptr(out2), dtype_code(out), int(write_x), stream_ptr())
+
+
+def embed_bigram(table: torch.Tensor, pairs: torch.Tensor, ctx, prev_token: torch.Tensor, buckets: int, mul_prev: int,
+                 mul_cur: int, out: torch.Tensor, copy: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t,:] = table[token,:] * scale + pairs[row,:] in float32, row = (previous token * mul_prev + token * mul_cur)
+    mod buckets, and row `buckets` for a sequence's first token.  prev_token int32 [slots]: the token before a step's
+    first, renewed with the step's last.  copy receives the same rows once more."""
+    _cuda(table, pairs, prev_token, out, copy)
+    V, E = table.shape
+    T = ctx.tokens.numel()
+    assert pairs.shape == (buckets + 1, E) and table.is_contiguous() and pairs.is_contiguous()
+    assert prev_token.dtype == torch.int32 and prev_token.dim() == 1 and prev_token.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous()
+    assert copy is None or (copy.dtype == torch.float32 and copy.shape == (T, E) and copy.is_contiguous())
+    call("gb_embed_bigram", ptr(table), dtype_code(table), ptr(pairs), dtype_code(pairs), ptr(ctx.tokens), ptr(ctx.pos),
+         ptr(ctx.seq_of), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(prev_token), T, E, V, int(buckets), int(mul_prev),
+         int(mul_cur), float(scale), ptr(out), ptr(copy), stream_ptr())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap tanh(x / cap) in place (float32)."""
+    _cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    call("gb_softcap", ptr(x), x.numel(), float(cap), stream_ptr())
+    return x
+
+
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, a: torch.Tensor,
                dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx,
                n_heads: int, n_kv_heads: int, dim: int, vdim: int, q_scale: float) -> torch.Tensor:
@@ -186,15 +329,19 @@ HEAD_GATES = {"sigmoid": 0, "silu": 1}
 
 
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                    n_heads: int, vdim: int, gate_function: str = "sigmoid") -> torch.Tensor:
-    """out[t,h,:] = o[t,h,:] / sqrt(mean(o[t,h,:]^2) + eps) * weight * f(gate[t,h,:]); o float32; f the sigmoid or SiLU."""
+                    n_heads: int, vdim: int, gate_function: str = "sigmoid", gate_first: bool = False) -> torch.Tensor:
+    """out[t,h,:] = o[t,h,:] / sqrt(mean(o[t,h,:]^2) + eps) * weight * f(gate[t,h,:]); o float32; f the sigmoid or SiLU.
+    weight: vdim entries that the heads share, or heads*vdim with a row per head.  gate_first: the gate comes before
+    the norm, out = y / sqrt(mean(y^2) + eps) * weight with y = o f(gate)."""
     _cuda(o, gate, weight, out)
     T = o.shape[0]
     assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
-    assert o.shape == gate.shape == out.shape == (T, n_heads * vdim) and weight.numel() == vdim
+    assert o.shape == gate.shape == out.shape == (T, n_heads * vdim) and weight.numel() in (vdim, n_heads * vdim)
+    assert weight.is_contiguous()
+    per_head = weight.numel() == n_heads * vdim and n_heads > 1
     call("gb_gated_head_norm", ptr(o), o.stride(0), ptr(gate), dtype_code(gate), gate.stride(0), ptr(weight),
          dtype_code(weight), float(eps), ptr(out), dtype_code(out), out.stride(0), T, n_heads, vdim,
-         HEAD_GATES[gate_function], stream_ptr())
+         HEAD_GATES[gate_function], int(per_head), int(bool(gate_first)), stream_ptr())
     return out
 
 
@@ -377,7 +524,7 @@ def moe_by_expert(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_g
     return out
 
 
-UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3}
+UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3, "tanh": 4}
 
 
 def unary_act_(x: torch.Tensor, activation: str) -> torch.Tensor:
@@ -690,18 +837,19 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
                      splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None,
                      rope: Optional[tuple] = None, keep_first: int = 0, head_pages: int = 0,
-                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
     the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
     where it fits) or the CUDA-core one (any head size that is a multiple of 16).
     rope = (k, v, inv_freq, rotary_dim, pairing), tensor-core kernel only: q, k and v are the
     unrotated projections; the kernel rotates q and k and writes k and v into the cache itself
     (k and v None: it reads another run's cache and only rotates q).
-    keep_first, head_pages, gate (CUDA-core kernel only): as attention_generic."""
+    keep_first, head_pages, gate, sink (CUDA-core kernel only): as attention_generic."""
     _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
-    kept = bool(keep_first or head_pages or gate is not None)
+    kept = bool(keep_first or head_pages or gate is not None or sink)
     assert not kept or (mma is False and rope is None)
-    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape == out.shape)
+    assert gate is None or gate.dtype == torch.bfloat16
+    per_head = _gate_per_head(gate, out, n_heads)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
@@ -731,7 +879,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
         call("gb_attention_decode_kept", ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
              ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
              float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), int(head_pages),
-             int(keep_first or 0), ptr(gate), 0 if gate is None else gate.stride(0), stream_ptr())
+             int(keep_first or 0), ptr(gate), 0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
         return out
     call(entry, ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
          ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
@@ -765,17 +913,18 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
                       tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
                       scale: float, tc: Optional[bool] = None, exact: bool = False, keep_first: int = 0, head_pages: int = 0,
-                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
     values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (the default where it
     fits), else on mma.sync; both take head sizes 64 and 128.  exact (mma.sync kernel only): the
     attention weights stay 32-bit, split into three bfloat16 terms for the product with the values.
-    keep_first, head_pages, gate (mma.sync kernel only): as attention_generic."""
+    keep_first, head_pages, gate, sink (mma.sync kernel only): as attention_generic."""
     _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache, gate)
-    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape == out.shape)
+    assert gate is None or gate.dtype == torch.bfloat16
+    per_head = _gate_per_head(gate, out, n_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
-    plain = not (exact or keep_first or head_pages or gate is not None)
+    plain = not (exact or keep_first or head_pages or gate is not None or sink)
     if tc is None:
         tc = attention_prefill_tc_supported(q, kcache, head_dim) and plain
     assert not tc or plain
@@ -788,7 +937,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
     call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
          tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
          ptr(vcache), int(window or 0), float(scale), int(bool(exact)), int(head_pages), int(keep_first or 0), ptr(gate),
-         0 if gate is None else gate.stride(0), stream_ptr())
+         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
     return out
 
 

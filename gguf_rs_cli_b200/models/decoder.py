@@ -137,6 +137,9 @@ class Decoder:
         """Keys and values for every run whose mixer keeps them, and the fixed-size state
         every run's mixer declares (named run<r>.<name>)."""
         layout = CacheLayout()
+        embed_states = getattr(self.embedding, "state_spec", None)
+        for name, sd in (embed_states() if embed_states else {}).items():
+            layout.states[f"embed.{name}"] = sd
         for r, run in enumerate(self.spec.schedule):
             mixer = self.layers[run.layer].mixer
             kv = mixer.kv_spec()
@@ -154,19 +157,28 @@ class Decoder:
                 gi, i = cache.group_of_run[src]
                 g = cache.groups[gi]
                 views.append(RunView(r, run.layer, run.cache_of is None, gi, g.k[i], None if g.v is None else g.v[i], g.ring_pages,
-                                      g.spec, g.head_pages))
+                                      g.spec, g.head_pages, run.add_input))
             else:
-                views.append(RunView(r, run.layer, False))
+                views.append(RunView(r, run.layer, False, add_input=run.add_input))
         return views
 
     # ---------------------------------------------------------------- forward
     def forward(self, ctx: StepContext, runs: List[RunView], want_rows: torch.Tensor) -> torch.Tensor:
         """Logits float32 [len(want_rows), V] at the packed token rows asked for."""
         make = getattr(self.embedding, "forward_stream", None)
-        stream = make(ctx.tokens, ctx) if make else Stream(self.embedding.forward(ctx.tokens, ctx))
+        x0 = None
+        if any(view.add_input for view in runs):
+            # runs that add the embedding's result again read it from a copy that the embedding writes beside x
+            x0 = ctx.ws.get("x0", (ctx.T, self.spec.hidden_size), torch.float32)
+            stream = self.embedding.forward_stream(ctx.tokens, ctx, copy=x0)
+        else:
+            stream = make(ctx.tokens, ctx) if make else Stream(self.embedding.forward(ctx.tokens, ctx))
         ctx.mark("embed")
         for view in runs:
             ctx.mark_detail = view.index == 0         # stages are stamped in the first run only, as the reference does
+            if view.add_input:
+                stream.more.append(x0)
+                stream.drop_shadow()
             self.layers[view.layer].block.forward(stream, ctx, view)
         ctx.mark_detail = True
         ctx.mark("layers")

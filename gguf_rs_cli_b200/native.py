@@ -140,13 +140,22 @@ _SIGNATURES = {
     "gb_swiglu": [_P, _L, _P, _I, _I, _I, _I, _P],
     "gb_zero_rows": [_P, _P, _I, _I, _P],
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
-    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _I, _I, _P, _I, _L, _P],
+    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _I, _I, _P, _I, _L, _I, _I,
+                             _P],
     "gb_add_dyt": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P],
     "gb_scale": [_P, _L, _F, _P],
     "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _L, _P],
     "gb_delta_rule": [_P, _P, _P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "gb_delta_rule_scratch_floats": [_I, _I, _I, _I, _I],
-    "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _I, _P],
+    "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P],
+    "gb_short_conv": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P],
+    "gb_softcap": [_P, _L, _F, _P],
+    "gb_token_shift_mix": [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "gb_wkv": [_P, _L, _P, _L, _P, _L, _I, _P, _I, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P],
+    "gb_ssd": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "gb_linear_walk_scratch_floats": [_I, _I, _I, _I],
+    "gb_add_rmsnorm_pair": [_P, _P, _I, _P, _I, _P, _I, _I, _P, _I, _I, _P, _P, _I, _F, _F, _P, _P, _I, _I, _P],
+    "gb_embed_bigram": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _F, _P, _P, _P],
     "gb_norm_residual_add": [_P, _P, _I, _L, _I, _I, _P, _I, _F, _P, _P],
     "gb_head_prep_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P, _L, _F, _P, _L, _P, _P, _P,
                               _I, _I, _I, _P, _P, _I, _P],
@@ -183,7 +192,8 @@ _SIGNATURES = {
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
     "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
-    "gb_attention_decode_kept": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _I, _I, _P, _L, _P],
+    "gb_attention_decode_kept": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _I, _I, _P, _L, _I, _I,
+                                 _P],
     "gb_attention_decode_mma": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
     "gb_attention_decode_mma_rope": [_P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I,
                                      _P, _P, _I, _P],
@@ -194,7 +204,7 @@ _SIGNATURES = {
     "gb_gemm_tc_set_stamps": [_P, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
-    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _I, _I, _P, _L, _P],
+    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _I, _I, _P, _L, _I, _I, _P],
     "gb_attention_prefill_supported": [_I, _I, _I],
     "gb_attention_prefill_tile": [],
     "gb_attention_prefill_tc": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _L, _I, _F, _P],
@@ -205,7 +215,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_gla_segment_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_gla_segment_floats": ctypes.c_longlong, "gb_linear_walk_scratch_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
@@ -241,7 +251,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2, "gb_moe_grouped": 4, "gb_moe_down": 2}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_short_conv": 2, "gb_wkv": 2, "gb_ssd": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2, "gb_moe_grouped": 4, "gb_moe_down": 2}
 
 
 def launch_count() -> int:

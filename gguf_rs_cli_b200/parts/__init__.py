@@ -1,4 +1,4 @@
-from . import attention, block, delta_rule, embedding, feed_forward, gla, latent_attention, norm, rotary  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta_rule, embedding, feed_forward, gla, latent_attention, norm, rotary, ssd, wkv  # noqa: F401  (register the built-in parts)
 from .base import HostBatch, Part, RunView, StepContext, Stream, Workspace, plan_key_of
 from .linear import Linear
 from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, register_block,

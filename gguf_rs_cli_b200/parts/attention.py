@@ -21,6 +21,11 @@ the rotation (`head_norm_eps`); the first positions of a sequence that stay visi
 sigmoid(W_g h) before the output projection (`out_gate`); and values mixed across layers (`v_mix`): the first
 layer that says so ("gives") leaves its values of the step's tokens for the later ones ("takes"), which cache
 v <- (1 - lambda) v + lambda v_first with a scalar lambda of their own.
+
+And for designs that smooth their projections over time and let a head attend to nothing: a short causal convolution
+per channel on q, k and v, directly behind the projection and before the rotation, without bias or activation (`conv`
+taps; the last taps - 1 projected rows are per-sequence state); a softmax whose denominator counts one more key of
+score 0 that has no value (`sink`); and a gate of one number per head instead of one per entry (`out_gate="head"`).
 """
 from __future__ import annotations
 
@@ -42,9 +47,11 @@ class Attention(Part):
     bias (q/k/v biases), shares_kv (default False), v_head_dim (default head_dim),
     qk_norm_eps (default None: no normalisation), q_temp (default None, or {"coef", "every"}),
     head_norm_eps (default None), keep_first (default 0), out_gate (default False), v_mix (None, "gives" or "takes"),
-    v_mix_optional (the folder may hold the scalar although nothing is mixed).
+    v_mix_optional (the folder may hold the scalar although nothing is mixed), conv (default None; taps of a short
+    convolution on q, k and v), sink (default False), out_gate "head": one gate per head.
     tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias;
-    with head_norm_eps q_norm, k_norm [hd]; with out_gate g [nh*vd, E]; with v_mix the scalar v_mix."""
+    with head_norm_eps q_norm, k_norm [hd]; with out_gate g [nh*vd, E] ("head": [nh, E]); with v_mix the scalar v_mix;
+    with conv q_conv, k_conv, v_conv [channels, taps]."""
 
     def __init__(self, spec, dtype, device, position=None):
         super().__init__(spec, dtype, device)
@@ -65,17 +72,31 @@ class Attention(Part):
         self.head_norm_eps = p.get("head_norm_eps")
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
         self.out_gate = bool(p.get("out_gate", False))
+        self.gate_per_head = p.get("out_gate") == "head"
+        self.conv = int(p.get("conv") or 1)
+        if not 1 <= self.conv <= 16:
+            raise ValueError(f"attention: a convolution of {self.conv} taps is not supported (1..16)")
+        self.sink = bool(p.get("sink", False))
         self.v_mix = p.get("v_mix") or None
         if self.v_mix not in (None, "gives", "takes"):
             raise ValueError(f"attention: v_mix {self.v_mix!r} is not one of None, 'gives', 'takes'")
         # heads with a norm of their own, a gate, kept first positions or mixed values: prepared by one kernel
         # (norm, rotation, mixing, cache write) and attended to with 32-bit weights
-        self.prepared = bool(self.head_norm_eps is not None or self.keep_first or self.out_gate or self.v_mix)
+        self.prepared = bool(self.head_norm_eps is not None or self.keep_first or self.out_gate or self.v_mix or self.conv > 1
+                             or self.sink)
+        # where the parts of the fused projection start: q, k, v and the gate, each at a multiple of 8 rows
+        self.off, rows = {}, 0
+        for n, size in (("q", self.nh * self.hd), ("k", self.nkv * self.hd), ("v", self.nkv * self.vd),
+                        ("g", (self.nh if self.gate_per_head else self.nh * self.vd) if self.out_gate else 0)):
+            self.off[n] = (rows + 7) // 8 * 8
+            rows = self.off[n] + size
+        self.gate_rows = rows - self.off["g"]
+        self.conv_channels = self.off["v"] + self.nkv * self.vd      # q, k, v and the empty rows between them
         # normalised q and k, a query temperature or values of their own size: the exact path
         self.exact = self.prepared or self.vd != self.hd or self.qk_norm_eps is not None or self.temp_coef != 0.0
         if self.prepared and (self.qk_norm_eps is not None or self.temp_coef != 0.0 or self.shares_kv or p.get("bias")):
-            raise ValueError("attention: head_norm_eps, keep_first, out_gate and v_mix go with none of qk_norm_eps, q_temp, "
-                             "shares_kv and biases")
+            raise ValueError("attention: head_norm_eps, keep_first, out_gate, v_mix, conv and sink go with none of qk_norm_eps, "
+                             "q_temp, shares_kv and biases")
         if self.exact and not self.prepared and (position is not None or self.shares_kv):
             raise ValueError("attention: qk_norm_eps, q_temp and v_head_dim go with neither a rotation nor shares_kv")
 
@@ -87,7 +108,7 @@ class Attention(Part):
         return KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
-        return {}
+        return {"conv": ((self.conv - 1, self.conv_channels), "float32")} if self.conv > 1 else {}
 
     def tensor_requests(self) -> List[TensorRequest]:
         E, t = self.p["hidden_size"], self.spec.tensors
@@ -100,7 +121,9 @@ class Attention(Part):
         if self.head_norm_eps is not None:
             req += [TensorRequest(t["q_norm"], (self.hd,), init="ones"), TensorRequest(t["k_norm"], (self.hd,), init="ones")]
         if self.out_gate:
-            req.append(TensorRequest(t["g"], (self.nh * self.vd, E)))
+            req.append(TensorRequest(t["g"], (self.gate_rows, E)))
+        if self.conv > 1:
+            req += [TensorRequest(t[n + "_conv"], (rows[n], self.conv), init="uniform:-0.6:0.6") for n in ("q", "k", "v")]
         if self.v_mix or self.p.get("v_mix_optional"):
             req.append(TensorRequest(t["v_mix"], (), optional=not self.v_mix, init="const:0.25" if self.v_mix else None))
         return req
@@ -127,12 +150,11 @@ class Attention(Part):
         names = ["q", "k", "v"] + (["g"] if self.out_gate else [])
         mats = [store.get(req[t[n]]) for n in names]
         dt = mats[0].dtype
-        parts, self.off, rows = [], {}, 0
+        parts, rows = [], 0
         for n, m in zip(names, mats):
-            pad = (rows + 7) // 8 * 8 - rows
+            pad = self.off[n] - rows
             if pad:
                 parts.append(torch.zeros(pad, m.shape[1], dtype=dt, device=m.device))
-            self.off[n] = rows + pad
             parts.append(m.to(dt))
             rows = self.off[n] + m.shape[0]
         pad = (rows + 7) // 8 * 8 - rows
@@ -145,6 +167,14 @@ class Attention(Part):
             self.q_norm, self.k_norm = store.get(req[t["q_norm"]]), store.get(req[t["k_norm"]])
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.k_norm = self.k_norm.to(self.q_norm.dtype)
+        self.taps = self.taps_t = None
+        if self.conv > 1:
+            # one convolution over all columns of q, k and v; the empty rows between them have taps of zero
+            self.taps = torch.zeros(self.conv_channels, self.conv, dtype=dt, device=mats[0].device)
+            for n in ("q", "k", "v"):
+                w = store.get(req[t[n + "_conv"]])
+                self.taps[self.off[n]:self.off[n] + w.shape[0]] = w.to(dt)
+            self.taps_t = self.taps.t().contiguous() if dt == torch.bfloat16 else None
         self.mix = 0.0
         if self.v_mix == "takes":
             lam = store.get(req[t["v_mix"]])
@@ -154,7 +184,7 @@ class Attention(Part):
 
     # ---- planning on the host
     def plan_key(self):
-        return ("attention", self.hd, self.window, self.exact, self.prepared, self.keep_first)
+        return ("attention", self.hd, self.vd, self.window, self.exact, self.prepared, self.keep_first)
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
@@ -200,9 +230,15 @@ class Attention(Part):
         proj = self.qkv(h, ctx)
         ctx.mark("qkv")
         off = self.off
+        gate = proj[:, off["g"]:off["g"] + self.gate_rows] if self.out_gate else None
+        if self.conv > 1:
+            conv = ctx.ws.get("attn.conv", (T, self.conv_channels), proj.dtype)
+            kernels.short_conv(proj[:, :self.conv_channels], self.taps, ctx.state(f"run{run.index}.conv"), ctx, conv,
+                               taps_t=self.taps_t)
+            proj = conv
+            ctx.mark("conv")
         q, k, v = (proj[:, off["q"]:off["q"] + nh * hd], proj[:, off["k"]:off["k"] + nkv * hd],
                    proj[:, off["v"]:off["v"] + nkv * vd])
-        gate = proj[:, off["g"]:off["g"] + nh * vd] if self.out_gate else None
         v_first = first_out = None
         if self.v_mix == "gives":
             first_out = ctx.shared[self.V_FIRST] = ctx.ws.get("attn.v_first", (T, nkv * vd), proj.dtype)
@@ -218,7 +254,7 @@ class Attention(Part):
         ctx.mark("heads")
         out = ctx.ws.get("attn.out", (T, nh * vd), ctx.dtype)
         tiles = ctx.plan_of(self).get("tiles")
-        kept = dict(keep_first=self.keep_first, head_pages=run.head_pages, gate=gate)
+        kept = dict(keep_first=self.keep_first, head_pages=run.head_pages, gate=gate, sink=self.sink)
         if not ctx.decode and tiles is not None and self._exact_tiled() and kernels.attention_prefill_supported(q, run.k, hd):
             # prompts, keys and values of 64 or 128 entries: the tiled kernel with 32-bit weights
             kernels.attention_prefill(q, out, nh, nkv, hd, tiles, ctx.cu, ctx.starts, ctx.qlens, table, run.ring_pages,

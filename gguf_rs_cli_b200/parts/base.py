@@ -110,6 +110,7 @@ class RunView:
     ring_pages: int = 1
     kv_spec: Optional[KVSpec] = None
     head_pages: int = 0           # table entries in front of the ring: pages of first positions that are kept for ever
+    add_input: bool = False       # the embedding's result is added to the stream once more before this run
 
 
 @dataclass
@@ -167,11 +168,15 @@ class Stream:
 
     A producer that adds its term to x itself (a product's residual epilogue, the embedding)
     may leave a shadow for the norm that follows: xb = bfloat16(x) and ssq [parts, T], partial
-    sums of x^2 per token.  The shadow is valid while nothing is pending and x is unchanged."""
+    sums of x^2 per token.  The shadow is valid while nothing is pending and x is unchanged.
+
+    `more` holds further terms [T, E] that wait beside `pending` (a layer whose mixer and feed-forward both read the
+    same x leaves two; a repeated pass adds the embedding's result); a norm that knows them adds them all at once."""
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.more: List[torch.Tensor] = []
         self.xb: Optional[torch.Tensor] = None
         self.ssq: Optional[torch.Tensor] = None
         self.ssq_parts = 0

@@ -103,3 +103,36 @@ class OutputNormBlock:
             stream.xb = ctx.ws.get("stream.xb", stream.x.shape, torch.bfloat16)
             kernels.norm_residual_add(stream.x, None, None, 1.0, xb=stream.xb)
         return stream.xb
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """x += mixer(norm_m(x)) + ff(norm_f(x)): both sublayers read norms of the same x.  The two norms are one pass over
+    the row (one root mean square, two weights); neither sum is done here: the mixer's term is left pending and the
+    feed-forward's beside it, and the next norm adds them in 32-bit while it normalises."""
+
+    norm_names = ("mixer", "feed_forward")
+    graph_class = ()
+
+    def __init__(self, mixer, feed_forward, norms):
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        if feed_forward is not None and not hasattr(norms["mixer"], "apply_pair"):
+            raise ValueError(f"parallel: the norm of kind {norms['mixer'].spec.kind!r} cannot give two norms of one row at once")
+
+    def forward(self, stream: Stream, ctx: StepContext, run: RunView) -> None:
+        if self.feed_forward is None:
+            h, h_ff = self.norms["mixer"].apply(stream, ctx), None
+        else:
+            h, h_ff = self.norms["mixer"].apply_pair(stream, self.norms["feed_forward"], ctx)
+        ctx.mark("norm")
+        term = self.mixer.forward(h, ctx, run)
+        if term.dim() != 2 or term.dtype != torch.float32:
+            raise RuntimeError("parallel: a mixer must give one 32-bit term [tokens, width]")
+        stream.pending = term
+        stream.drop_shadow()
+        if self.feed_forward is not None:
+            term = self.feed_forward.forward(h_ff, ctx)
+            if term.dim() != 2:
+                raise RuntimeError("parallel: a feed-forward must give one term [tokens, width]")
+            stream.more.append(term)
+            ctx.mark("ff")

@@ -3,7 +3,7 @@
 when the folder has no matrix of its own (src/model/llama.rs:124)."""
 from __future__ import annotations
 
-from typing import List
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -31,9 +31,12 @@ class Embedding(Part):
         x = ctx.ws.get("x", (tokens.numel(), self.p["hidden_size"]), torch.float32)
         return kernels.embed(self.weight, tokens, x, float(self.p.get("scale", 1.0)))
 
-    def forward_stream(self, tokens: torch.Tensor, ctx: StepContext) -> Stream:
+    def forward_stream(self, tokens: torch.Tensor, ctx: StepContext, copy: Optional[torch.Tensor] = None) -> Stream:
         """The residual stream of a step; in bfloat16 mode with the shadow (bfloat16 copy and sums of
-        squares per token) that lets the first norm be deferred into the product after it."""
+        squares per token) that lets the first norm be deferred into the product after it.  copy: a second
+        float32 buffer [T, E] that receives the same rows (for models that add them to the stream again)."""
+        if copy is not None:
+            kernels.embed(self.weight, tokens, copy, float(self.p.get("scale", 1.0)))
         if ctx.dtype != torch.bfloat16 or tokens.numel() > FUSE_MAX_TOKENS:
             return Stream(self.forward(tokens, ctx))
         T, E = tokens.numel(), self.p["hidden_size"]
@@ -45,11 +48,44 @@ class Embedding(Part):
         return stream
 
 
+@register_embedding("embedding_bigram")
+class HashedPairEmbedding(Embedding):
+    """The token's row plus a row of a second table that the pair (previous token, token) chooses by a hash:
+    row (previous * mul_prev + token * mul_cur) mod buckets, and the table's last row (number `buckets`) for a
+    sequence's first token.  The previous token of a step's first token is per-sequence state.
+    params: vocab_size, hidden_size, buckets, mul_prev, mul_cur, scale (default 1, of the token's row only).
+    tensors: weight [V, E], pairs [buckets + 1, E]."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if int(self.p["buckets"]) <= 0:
+            raise ValueError(f"embedding_bigram: buckets must be positive, got {self.p['buckets']!r}")
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return super().tensor_requests() + [TensorRequest(self.spec.tensors["pairs"], (self.p["buckets"] + 1, self.p["hidden_size"]))]
+
+    def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        return {"prev": ((), "int32")}
+
+    def load(self, store: WeightStore) -> None:
+        reqs = self.tensor_requests()
+        self.weight, self.pairs = store.get(reqs[0]), store.get(reqs[1])
+
+    def forward(self, tokens: torch.Tensor, ctx: StepContext, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = ctx.ws.get("x", (tokens.numel(), self.p["hidden_size"]), torch.float32)
+        return kernels.embed_bigram(self.weight, self.pairs, ctx, ctx.state("embed.prev"), self.p["buckets"], self.p["mul_prev"],
+                                    self.p["mul_cur"], x, copy=copy, scale=float(self.p.get("scale", 1.0)))
+
+    def forward_stream(self, tokens: torch.Tensor, ctx: StepContext, copy: Optional[torch.Tensor] = None) -> Stream:
+        return Stream(self.forward(tokens, ctx, copy=copy))
+
+
 @register_head("lm_head")
 class LMHead(Part):
     """params: vocab_size, hidden_size, tied_to (the tensor that stands in when the folder has no
     head matrix of its own, or None), tied (the configuration says the head is the embedding: the
-    random-weights mode then writes no matrix for it), logit_scale (default 1: the logits are multiplied by it).
+    random-weights mode then writes no matrix for it), logit_scale (default 1: the logits are multiplied by it),
+    softcap (default None; c: the logits become c tanh(logits / c), after the scale).
     tensors: weight [V, E].  As in the reference, presence decides: a folder that has the matrix
     uses it, one that lacks it uses `tied_to` (src/model/llama.rs:124)."""
 
@@ -68,4 +104,7 @@ class LMHead(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         logits = self.proj(h, ctx, out_dtype=torch.float32)
         scale = float(self.p.get("logit_scale", 1.0))
-        return logits if scale == 1.0 else kernels.scale_(logits, scale)
+        if scale != 1.0:
+            kernels.scale_(logits, scale)
+        cap = self.p.get("softcap")
+        return kernels.softcap_(logits, float(cap)) if cap else logits

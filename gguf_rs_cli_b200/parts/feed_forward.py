@@ -18,7 +18,8 @@ from .registry import register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
-    """params: hidden_size, intermediate_size, activation ("silu" or "gelu_tanh").
+    """params: hidden_size, intermediate_size, activation ("silu" or "gelu_tanh"), term_f32 (default False: the down
+    product's result, which is added to the residual stream, is kept in 32-bit also where the products run in bfloat16).
     tensors: gate [F, E], up [F, E], down [E, F]."""
 
     def __init__(self, spec, dtype, device):
@@ -67,7 +68,7 @@ class GatedMLP(Part):
         else:
             kernels.swiglu(self.gate_up(h, ctx), act, self.activation)
         ctx.mark("gate_up")
-        term = self.down(act, ctx, residual=residual)
+        term = self.down(act, ctx, residual=residual, out_dtype=torch.float32 if self.p.get("term_f32") else None)
         ctx.mark("down")
         return term
 
