@@ -4,7 +4,7 @@ one B200.  Prints one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--no-points] [--prompt-steps 128,256] [--shape 8b|1b|13b]
-                    [--design debonex|dilalix [--sizes 1b,8b]]
+                    [--design debonex|dilalix|nazerax [--sizes 1b,8b]]
 
 `value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
 device with CUDA events around K decode steps (each step: index arrays host to
@@ -327,7 +327,33 @@ def llama_config(z):
             "hidden_act": "silu"}
 
 
-DESIGN_CONFIGS = {"debonex": debonex_config, "dilalix": dilalix_config}
+def dilalix_dense_config(z):
+    """dilalix_config with a dense feed-forward in every layer: what Nazerax, which has no routed experts, stands beside."""
+    raw = dilalix_config(z)
+    raw["layers"] = [{**layer, "mlp": {"kind": "dense", "ff": z["ff"]}} for layer in raw["layers"]]
+    return raw
+
+
+def nazerax_config(z):
+    """A state-space layer (as many heads as the others, state and values of z["head"] entries: the walk's shape of the
+    other designs' recurrent layers), a wkv layer, attention (window of 1,024, a convolution of 4 taps, half of each head
+    rotated, one gate per head, a sink), a wkv layer; gated SiLU feed-forwards; a pair table of 16,384 rows; no repeated
+    stretch, so that the number of layer runs equals the other models'."""
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    ssm = {"heads": z["heads"], "vdim": z["head"], "state": z["head"], "groups": 1, "norm_groups": 1, "conv": 4}
+    wkv = {"heads": z["heads"], "dim": z["head"]}
+    attn = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5, "conv": 4,
+            "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": z["head"] // 2}}
+    pattern = [{"type": "mamba2", "mixer": ssm, "mlp": mlp}, {"type": "wkv", "mixer": wkv, "mlp": mlp},
+               {"type": "attention", "mixer": attn, "mlp": mlp}, {"type": "wkv", "mixer": wkv, "mlp": mlp}]
+    return {"architecture": "Nazerax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": 16384, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [pattern[i % 4] for i in range(z["layers"])]}
+
+
+DESIGN_CONFIGS = {"debonex": debonex_config, "dilalix": dilalix_config, "nazerax": nazerax_config}
+# the closest of the other designs (a recurrent rule and attention), which a design is measured beside
+CLOSEST = {"dilalix": ("debonex", debonex_config), "nazerax": ("dilalix-dense", dilalix_dense_config)}
 
 
 def stage_times(llm, lens, starts=0, reps=3):
@@ -387,8 +413,8 @@ def run_design(args, pk):
         z = DESIGN_SIZES[name]
         row = {"config": z}
         arms = [(args.design, DESIGN_CONFIGS[args.design](z))]
-        if args.design != "debonex":
-            arms.append(("debonex", debonex_config(z)))          # the closest of the other designs: a recurrent rule and attention
+        if args.design in CLOSEST:
+            arms.append((CLOSEST[args.design][0], CLOSEST[args.design][1](z)))
         for arm, raw in arms + [("llama", llama_config(z))]:
             llm = from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
             torch.cuda.synchronize()

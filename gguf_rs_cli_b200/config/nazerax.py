@@ -98,7 +98,7 @@ def _read_mixer(kind: str, raw, where: str) -> Dict[str, Any]:
     m["mask"] = m["rot"] = None
     if raw.get("mask") is not None:
         m["mask"] = {"size": _get(raw["mask"], "size", where + ".mask")}
-    if raw.get("rot") is not None:
+    if raw.get("rot") is not None and raw["rot"].get("dims") != 0:          # no entries to rotate: no rotation
         m["rot"] = {"base": _get(raw["rot"], "base", where + ".rot", float), "dims": _get(raw["rot"], "dims", where + ".rot")}
         if m["rot"]["dims"] % 2 or m["rot"]["dims"] > m["dim"]:
             raise ConfigError(f"config.json: {where}.rot.dims {m['rot']['dims']} must be even and at most dim {m['dim']}")

@@ -461,6 +461,39 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, long long ld
     }
 }
 
+// The same for long heads (a norm over a whole row in one or a few parts): one block per (token, head).
+__global__ void __launch_bounds__(256) gated_head_norm_block_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ gate,
+                                                                    int gate_dtype, long long ldg, const void* __restrict__ w, int w_dtype,
+                                                                    float eps, void* __restrict__ out, int out_dtype, long long ld_out, int H,
+                                                                    int Dv, int gate_act, int w_per_head, int gate_first) {
+    __shared__ float red[8];
+    const long long t = blockIdx.x / H;
+    const int h = int(blockIdx.x - t * H);
+    const float* orow = o + t * ldo + size_t(h) * Dv;
+    const size_t grow = size_t(t) * ldg + size_t(h) * Dv, wrow = w_per_head ? size_t(h) * Dv : 0;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        float y = orow[d];
+        if (gate_first) {
+            const float gt = gb_load(gate, gate_dtype, grow + d);
+            y *= (gate_act ? gt : 1.f) / (1.f + expf(-gt));
+        }
+        ss = fmaf(y, y, ss);
+    }
+    ss = gb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+    const float rms = sqrtf(tot / float(Dv) + eps);
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        const float gt = gb_load(gate, gate_dtype, grow + d);
+        const float f = (gate_act ? gt : 1.f) / (1.f + expf(-gt));
+        const float wv = gb_load(w, w_dtype, wrow + d);
+        gb_store(out, out_dtype, size_t(t) * ld_out + size_t(h) * Dv + d, gate_first ? orow[d] * f / rms * wv : orow[d] / rms * wv * f);
+    }
+}
+
 GB_API int gb_gated_head_norm(const float* o, long long ldo, const void* gate, int gate_dtype, long long ldg, const void* w,
                               int w_dtype, float eps, void* out, int out_dtype, long long ld_out, int T, int H, int Dv,
                               int gate_act, int w_per_head, int gate_first, cudaStream_t stream) {
@@ -469,6 +502,12 @@ GB_API int gb_gated_head_norm(const float* o, long long ldo, const void* gate, i
     GB_REQUIRE(gate_act == 0 || gate_act == 1, "gb_gated_head_norm: unknown gate function %d", gate_act);
     if (T == 0) return 0;
     const long long items = (long long)T * H;
+    if (Dv >= 1024 && items <= 0x7fffffffLL) {
+        gated_head_norm_block_kernel<<<unsigned(items), 256, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out, out_dtype,
+                                                                          ld_out, H, Dv, gate_act, w_per_head, gate_first);
+        GB_LAUNCH_OK("gb_gated_head_norm");
+        return 0;
+    }
     gated_head_norm_kernel<<<unsigned((items + 3) / 4), 128, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out,
                                                                           out_dtype, ld_out, items, H, Dv, gate_act, w_per_head, gate_first);
     GB_LAUNCH_OK("gb_gated_head_norm");

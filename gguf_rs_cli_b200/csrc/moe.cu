@@ -301,6 +301,24 @@ __global__ void unary_act_kernel(void* __restrict__ x, int dtype, long long n, i
     if (i < n) gb_store(x, dtype, size_t(i), gb_act_unary(gb_load(x, dtype, size_t(i)), act));
 }
 
+// The same for a block of `cols` columns of rows that lie ld entries apart.
+__global__ void unary_act_rows_kernel(void* __restrict__ x, int dtype, long long n, int cols, long long ld, int act) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t at = size_t(i / cols) * ld + size_t(i % cols);
+    gb_store(x, dtype, at, gb_act_unary(gb_load(x, dtype, at), act));
+}
+
+GB_API int gb_unary_act_rows(void* x, int dtype, int rows, int cols, long long ld, int act, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && act >= 1 && act <= 4, "gb_unary_act_rows: bad dtype or activation %d", act);
+    GB_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, "gb_unary_act_rows: bad sizes rows=%d cols=%d ld=%lld", rows, cols, ld);
+    const long long n = (long long)rows * cols;
+    if (n == 0) return 0;
+    unary_act_rows_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(x, dtype, n, cols, ld, act);
+    GB_LAUNCH_OK("gb_unary_act_rows");
+    return 0;
+}
+
 // x <- act(x) entry by entry, in place (contiguous).  act: GbGateAct or GbUnaryAct.
 GB_API int gb_unary_act(void* x, int dtype, long long n, int act, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && act >= 1 && act <= 4, "gb_unary_act: bad dtype or activation %d", act);

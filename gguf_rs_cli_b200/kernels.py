@@ -528,10 +528,14 @@ UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3, "tanh": 4}
 
 
 def unary_act_(x: torch.Tensor, activation: str) -> torch.Tensor:
-    """x <- act(x) in place; gelu is the exact form 0.5 z (1 + erf(z / sqrt 2))."""
+    """x <- act(x) in place; gelu is the exact form 0.5 z (1 + erf(z / sqrt 2)).  x: contiguous, or a block of columns
+    of a row-major buffer."""
     _cuda(x)
-    assert x.is_contiguous()
-    call("gb_unary_act", ptr(x), dtype_code(x), x.numel(), UNARY_ACTS[activation], stream_ptr())
+    if x.is_contiguous():
+        call("gb_unary_act", ptr(x), dtype_code(x), x.numel(), UNARY_ACTS[activation], stream_ptr())
+    else:
+        assert x.dim() == 2 and x.stride(1) == 1
+        call("gb_unary_act_rows", ptr(x), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), UNARY_ACTS[activation], stream_ptr())
     return x
 
 

@@ -167,6 +167,7 @@ _SIGNATURES = {
     "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
     "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P],
     "gb_unary_act": [_P, _I, _L, _I, _P],
+    "gb_unary_act_rows": [_P, _I, _I, _I, _L, _I, _P],
     "gb_moe_grouped_supported": [_I, _I],
     "gb_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "gb_moe_gather_rows": [_P, _L, _I, _I, _I, _P, _P, _P],

@@ -11,6 +11,10 @@ multiplied by a weight (one per head and entry) and by SiLU(W_g blend_g), and pr
 decay's low-rank pair is the files' own size.  The last row of h is per-sequence state beside S.  The reference has
 no such mixer (src/model/llama.rs has attention only).
 
+Steps of a few tokens run r, k, v, g and w1 as one product: the five blends stacked as rows against the five matrices
+stacked as columns, of whose 25 blocks the five on the diagonal are used.  Such a step is bound by reading the
+weights, which this does once and in one launch; longer steps, bound by arithmetic, run a product per blend.
+
 The recurrence is the walk that gated linear attention uses, reading the state before the token's own update
 (csrc/wkv.cu, csrc/gla.cu).  Decays, their exponentials, the bonus and the state are 32-bit.
 """
@@ -28,6 +32,7 @@ from .linear import Linear
 from .registry import register_mixer
 
 BLENDS = ("r", "k", "v", "g", "w")
+STACK_MAX_TOKENS = 24            # 5 * 24 rows: still one tile of tokens for the tensor-core product
 
 
 @register_mixer("wkv")
@@ -65,6 +70,22 @@ class TimeMix(Part):
         self.mu = torch.stack([w["mu_" + s].to(dt) for s in BLENDS]).contiguous()
         self.proj = {s: Linear(w[s], name="wkv." + s) for s in ("r", "k", "v", "g")}
         self.w1, self.w2 = Linear(w["w1"], name="wkv.w1"), Linear(w["w2"], name="wkv.w2")
+        self.rank = w["w1"].shape[0]
+        # all five matrices as one, each part starting at a multiple of 8 rows, for steps of a few tokens
+        self.stack, self.off = None, {}
+        if dt == torch.bfloat16 and self.E % 8 == 0 and w["r"].is_cuda:
+            parts, rows = [], 0
+            for s in ("r", "k", "v", "g", "w1"):
+                pad = (rows + 7) // 8 * 8 - rows
+                if pad:
+                    parts.append(torch.zeros(pad, self.E, dtype=dt, device=w[s].device))
+                self.off[s] = rows + pad
+                parts.append(w[s].to(dt))
+                rows = self.off[s] + w[s].shape[0]
+            pad = (rows + 7) // 8 * 8 - rows
+            if pad:
+                parts.append(torch.zeros(pad, self.E, dtype=dt, device=w["r"].device))
+            self.stack = Linear(torch.cat(parts, dim=0).contiguous(), name="wkv.stack")
         self.w0 = w["w0"].contiguous()
         self.u = w["u"].to(self.w0.dtype).contiguous()
         self.norm_weight = w["norm"].contiguous()
@@ -77,9 +98,16 @@ class TimeMix(Part):
         blends = ctx.ws.get("wkv.blends", (len(BLENDS), T, self.E), ctx.dtype)
         kernels.token_shift_mix(h, self.mu, ctx.state(f"run{run.index}.prev"), ctx, blends)
         ctx.mark("shift")
-        r, k, v, g = (self.proj[s](blends[i], ctx) for i, s in enumerate(("r", "k", "v", "g")))
+        n = H * D
+        if self.stack is not None and T <= STACK_MAX_TOKENS:
+            both = self.stack(blends.view(len(BLENDS) * T, self.E), ctx)
+            r, k, v, g = (both[i * T:(i + 1) * T, self.off[s]:self.off[s] + n] for i, s in enumerate(("r", "k", "v", "g")))
+            low = kernels.unary_act_(both[4 * T:5 * T, self.off["w1"]:self.off["w1"] + self.rank], "tanh")
+        else:
+            r, k, v, g = (self.proj[s](blends[i], ctx) for i, s in enumerate(("r", "k", "v", "g")))
+            low = self.w1(blends[4], ctx, activation="tanh")
         # the decay's second product keeps 32-bit results: their exponentials enter the recurrence
-        a = self.w2(self.w1(blends[4], ctx, activation="tanh"), ctx, out_dtype=torch.float32)
+        a = self.w2(low, ctx, out_dtype=torch.float32)
         ctx.mark("projections")
         read = ctx.ws.get("wkv.read", (T, H * D), torch.float32)
         kernels.wkv(r, k, v, a, self.w0, self.u, ctx.state(f"run{run.index}.S"), read, ctx, H, D)

@@ -129,7 +129,8 @@ def test_short_convolution_with_bias_and_without_activation(C, K, bias, act, dty
         assert_close(torch.cat(got[i]), want[i].float(), dtype, f"convolution C={C} taps={K} sequence {i}")
 
 
-@pytest.mark.parametrize("H,Dv,per_head,first", [(3, 20, True, False), (2, 36, False, True), (4, 64, True, True), (1, 300, True, True)])
+@pytest.mark.parametrize("H,Dv,per_head,first", [(3, 20, True, False), (2, 36, False, True), (4, 64, True, True), (1, 300, True, True),
+                                                 (1, 2048, True, True), (2, 1500, True, False), (3, 1024, False, True)])
 def test_head_norm_with_rows_of_weights_and_gate_in_front(H, Dv, per_head, first):
     from gguf_rs_cli_b200 import kernels
     g = torch.Generator().manual_seed(H * Dv)
@@ -385,6 +386,35 @@ def test_long_decoding_through_a_ring_that_goes_round(name, dtype):
             assert_close(got[0], want[i], dtype, f"{name} position {i}")
     eng.close(s)
     eng.cache.check()
+
+
+ODD = {
+    "architecture": "Nazerax", "vocab": 61, "width": 50, "norm": {"eps": 1e-4}, "logit_softcap": 4.0,
+    "embedding": {"bigram": {"buckets": 7, "mul_prev": 3, "mul_cur": 1}}, "loop": {"start": 0, "stop": 3, "times": 2},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 5, "dim": 7}, "mlp": {"kind": "dense", "ff": 33}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 10, "vdim": 7, "conv": 5, "scale": 0.5, "mask": {"size": 1},
+                                        "rot": {"base": 10.0, "dims": 2}}, "mlp": {"kind": "dense", "ff": 21}},
+        {"type": "mamba2", "mixer": {"heads": 3, "vdim": 5, "state": 9, "groups": 3, "norm_groups": 5, "conv": 1}, "mlp": None},
+    ],
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_that_fit_no_fast_kernel(dtype):
+    """Odd sizes everywhere (no multiple of 8, of 4 or even of 2 where the design allows it), a window of one position, a
+    state-space layer without a convolution, a rank of one: a prompt, then single tokens, two requests together."""
+    from gguf_rs_cli_b200.engine.step import Engine
+    w = make_weights(ODD, {0: 1}, seed=5)
+    seqs = [torch.randint(0, ODD["vocab"], (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (75, 12)]
+    want = [P.forward(ODD, as_plain(w), s).float() for s in seqs]
+    eng = Engine(build(ODD, w, dtype).model, n_tokens=512, n_slots=2)
+    slots = [eng.open(), eng.open()]
+    got = eng.step([entry(slots[0], seqs[0][:66], range(66)), entry(slots[1], seqs[1][:3], range(3))])
+    assert_close(got, torch.cat([want[0][:66], want[1][:3]]), dtype, "two prompts of odd sizes")
+    for i in range(9):
+        got = eng.step([entry(slots[0], [seqs[0][66 + i]], [0]), entry(slots[1], [seqs[1][3 + i]], [0])])
+        assert_close(got, torch.stack([want[0][66 + i], want[1][3 + i]]), dtype, f"single tokens, step {i}")
 
 
 @pytest.mark.parametrize("kind", ["wkv", "mamba2", "attention", "bare"])
