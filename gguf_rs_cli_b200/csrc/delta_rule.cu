@@ -462,11 +462,11 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, long long ld
 }
 
 // The same for long heads (a norm over a whole row in one or a few parts): one block per (token, head).
-__global__ void __launch_bounds__(256) gated_head_norm_block_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ gate,
+__global__ void __launch_bounds__(1024) gated_head_norm_block_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ gate,
                                                                     int gate_dtype, long long ldg, const void* __restrict__ w, int w_dtype,
                                                                     float eps, void* __restrict__ out, int out_dtype, long long ld_out, int H,
                                                                     int Dv, int gate_act, int w_per_head, int gate_first) {
-    __shared__ float red[8];
+    __shared__ float red[32];
     const long long t = blockIdx.x / H;
     const int h = int(blockIdx.x - t * H);
     const float* orow = o + t * ldo + size_t(h) * Dv;
@@ -503,7 +503,7 @@ GB_API int gb_gated_head_norm(const float* o, long long ldo, const void* gate, i
     if (T == 0) return 0;
     const long long items = (long long)T * H;
     if (Dv >= 1024 && items <= 0x7fffffffLL) {
-        gated_head_norm_block_kernel<<<unsigned(items), 256, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out, out_dtype,
+        gated_head_norm_block_kernel<<<unsigned(items), Dv >= 4096 ? 1024 : Dv >= 2048 ? 512 : 256, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out, out_dtype,
                                                                           ld_out, H, Dv, gate_act, w_per_head, gate_first);
         GB_LAUNCH_OK("gb_gated_head_norm");
         return 0;

@@ -11,7 +11,7 @@
 #include "common.cuh"
 #include "linear_walk.h"
 
-// One block per token.  out holds n_mix blends [T, E] one after the other (mix_stride elements apart); mu [n_mix, E].
+// blockIdx.x is the token, blockIdx.y a slice of blockDim.x entries of its row.  out holds n_mix blends [T, E] one after the other (mix_stride elements apart); mu [n_mix, E].
 // The block of a sequence's first token of the step reads the carried row and then replaces it with the step's last.
 __global__ void __launch_bounds__(256) token_shift_mix_kernel(const void* __restrict__ h, int dtype, long long ldh, int E,
                                                               const void* __restrict__ mu, int mu_dtype, int n_mix,
@@ -20,16 +20,17 @@ __global__ void __launch_bounds__(256) token_shift_mix_kernel(const void* __rest
                                                               const int* __restrict__ qlens, void* __restrict__ out,
                                                               long long mix_stride) {
     const int t = blockIdx.x, b = seq_of[t];
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= E) return;
     if (b < 0) {
-        for (int s = 0; s < n_mix; ++s)
-            for (int i = threadIdx.x; i < E; i += blockDim.x) gb_store(out, dtype, size_t(s) * mix_stride + size_t(t) * E + i, 0.f);
+        for (int s = 0; s < n_mix; ++s) gb_store(out, dtype, size_t(s) * mix_stride + size_t(t) * E + i, 0.f);
         return;
     }
     const int first = cu[b], slot = slots[b];
     const bool head = t == first;
     float* keep = carried + size_t(slot) * E;
     const size_t last = size_t(first + qlens[b] - 1) * ldh;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    {
         const float cur = gb_load(h, dtype, size_t(t) * ldh + i);
         float before;
         if (head) {
@@ -52,7 +53,8 @@ GB_API int gb_token_shift_mix(const void* h, int dtype, long long ldh, int T, in
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(mu_dtype), "gb_token_shift_mix: bad dtype");
     GB_REQUIRE(E > 0 && n_mix > 0 && ldh >= E && carried, "gb_token_shift_mix: bad sizes E=%d blends=%d", E, n_mix);
     if (T == 0) return 0;
-    token_shift_mix_kernel<<<T, 256, 0, stream>>>(h, dtype, ldh, E, mu, mu_dtype, n_mix, carried, seq_of, cu, slots, qlens, out,
+    GB_REQUIRE((E + 255) / 256 <= 65535, "gb_token_shift_mix: rows of %d entries are too long", E);
+    token_shift_mix_kernel<<<dim3(T, (E + 255) / 256), 256, 0, stream>>>(h, dtype, ldh, E, mu, mu_dtype, n_mix, carried, seq_of, cu, slots, qlens, out,
                                                   (long long)T * E);
     GB_LAUNCH_OK("gb_token_shift_mix");
     return 0;
