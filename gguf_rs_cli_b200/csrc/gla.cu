@@ -75,9 +75,14 @@ __device__ __forceinline__ void gla_cp16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
+// Blocks of the walk that share an SM when a lane holds up to 32 rows of S: a thread's registers are bounded so that this
+// many fit.  Unbounded, the instance that reads the state first takes 187 registers and two blocks fit, the other 168 and
+// three; a prompt of 2,048 tokens, 16 heads of 128 x 128, both passes: 0.77 ms with two blocks, 0.62 with three, 0.60 with four.
+#define GLA_WALK_BLOCKS 4
+
 // BEFORE: what a token reads is the state as the token before it left it (its own k v^T is not in it).
 template <int NR, bool BEFORE>
-__global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
+__global__ void __launch_bounds__(128, NR <= 32 ? GLA_WALK_BLOCKS : 1) gla_walk_kernel(const GlaWalkParams p) {
     extern __shared__ __align__(16) float gla_sm[];
     float* sm = gla_sm;
     const int b = p.mode ? blockIdx.x / p.n_seg : blockIdx.x, seg = p.mode ? blockIdx.x % p.n_seg : 0, h = blockIdx.y;
