@@ -45,6 +45,60 @@ __global__ void __launch_bounds__(256) token_shift_mix_kernel(const void* __rest
     }
 }
 
+// The same for bfloat16 rows whose length and distance are multiples of 8: a thread takes 8 neighbouring entries with
+// 16-byte loads and stores (one entry a thread moves 0.25 of the copy bandwidth, this 0.6).
+__device__ __forceinline__ void ts_unpack8(const uint4& raw, float* f) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(p[j]);
+        f[2 * j] = a.x;
+        f[2 * j + 1] = a.y;
+    }
+}
+
+__global__ void __launch_bounds__(128) token_shift_mix_vec_kernel(const __nv_bfloat16* __restrict__ h, long long ldh, int E,
+                                                                  const __nv_bfloat16* __restrict__ mu, int n_mix,
+                                                                  float* __restrict__ carried, const int* __restrict__ seq_of,
+                                                                  const int* __restrict__ cu, const int* __restrict__ slots,
+                                                                  const int* __restrict__ qlens, __nv_bfloat16* __restrict__ out,
+                                                                  long long mix_stride) {
+    const int t = blockIdx.x, b = seq_of[t];
+    const int i = 8 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (i >= E) return;
+    if (b < 0) {
+        for (int s = 0; s < n_mix; ++s)
+            *reinterpret_cast<uint4*>(out + size_t(s) * mix_stride + size_t(t) * E + i) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const int first = cu[b];
+    float cur[8], before[8];
+    ts_unpack8(*reinterpret_cast<const uint4*>(h + size_t(t) * ldh + i), cur);
+    if (t == first) {
+        float* keep = carried + size_t(slots[b]) * E + i;
+        float last[8];
+        ts_unpack8(*reinterpret_cast<const uint4*>(h + size_t(first + qlens[b] - 1) * ldh + i), last);
+        const float4 k0 = *reinterpret_cast<const float4*>(keep), k1 = *reinterpret_cast<const float4*>(keep + 4);
+        before[0] = k0.x; before[1] = k0.y; before[2] = k0.z; before[3] = k0.w;
+        before[4] = k1.x; before[5] = k1.y; before[6] = k1.z; before[7] = k1.w;
+        *reinterpret_cast<float4*>(keep) = make_float4(last[0], last[1], last[2], last[3]);
+        *reinterpret_cast<float4*>(keep + 4) = make_float4(last[4], last[5], last[6], last[7]);
+    } else {
+        ts_unpack8(*reinterpret_cast<const uint4*>(h + size_t(t - 1) * ldh + i), before);
+    }
+    for (int s = 0; s < n_mix; ++s) {
+        float m[8];
+        ts_unpack8(*reinterpret_cast<const uint4*>(mu + size_t(s) * E + i), m);
+        uint4 packed;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            o[j] = __floats2bfloat162_rn(fmaf(before[2 * j] - cur[2 * j], m[2 * j], cur[2 * j]),
+                                         fmaf(before[2 * j + 1] - cur[2 * j + 1], m[2 * j + 1], cur[2 * j + 1]));
+        *reinterpret_cast<uint4*>(out + size_t(s) * mix_stride + size_t(t) * E + i) = packed;
+    }
+}
+
 // h [T, E] rows ldh apart; mu [n_mix, E]; carried float32 [slots, E] (zero for a sequence that starts), read and renewed;
 // out [n_mix, T, E] of h's dtype.
 GB_API int gb_token_shift_mix(const void* h, int dtype, long long ldh, int T, int E, const void* mu, int mu_dtype, int n_mix,
@@ -54,6 +108,15 @@ GB_API int gb_token_shift_mix(const void* h, int dtype, long long ldh, int T, in
     GB_REQUIRE(E > 0 && n_mix > 0 && ldh >= E && carried, "gb_token_shift_mix: bad sizes E=%d blends=%d", E, n_mix);
     if (T == 0) return 0;
     GB_REQUIRE((E + 255) / 256 <= 65535, "gb_token_shift_mix: rows of %d entries are too long", E);
+    const auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (dtype == GB_BF16 && mu_dtype == GB_BF16 && E % 8 == 0 && ldh % 8 == 0 && aligned16(h) && aligned16(mu) && aligned16(out) &&
+        aligned16(carried)) {
+        token_shift_mix_vec_kernel<<<dim3(T, (E / 8 + 127) / 128), 128, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(h), ldh, E, static_cast<const __nv_bfloat16*>(mu), n_mix, carried, seq_of, cu, slots,
+            qlens, static_cast<__nv_bfloat16*>(out), (long long)T * E);
+        GB_LAUNCH_OK("gb_token_shift_mix");
+        return 0;
+    }
     token_shift_mix_kernel<<<dim3(T, (E + 255) / 256), 256, 0, stream>>>(h, dtype, ldh, E, mu, mu_dtype, n_mix, carried, seq_of, cu, slots, qlens, out,
                                                   (long long)T * E);
     GB_LAUNCH_OK("gb_token_shift_mix");
