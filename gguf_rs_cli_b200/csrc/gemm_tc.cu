@@ -633,6 +633,40 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
     }
 }
 
+// G products of equal sizes in one launch of the kernel that pairs two SMs: out[g] = X[g] W[g]^T.
+// X: bf16 [G, group_t, K] (rows ldx apart, the problems group_t rows apart), W: bf16 [G * N, K] (problem g's features from
+// row g * N on), out: bf16 [G, group_t, N] (rows ldo apart).  group_t is a multiple of 256; rows of X that a caller pads
+// a problem with give rows of out that it does not read.  N need not be a multiple of the tile's 256 features: what a
+// tile computes beyond N (with the next problem's features) is cut off by the result's tensor map.  Small products
+// gain from this: G times the tiles in one grid, so that one tile's epilogue runs under another's main loop.
+GB_API int gb_gemm_tc_grouped(const void* X, long long ldx, const void* W, long long ldw, void* out, long long ldo, int G,
+                              int group_t, int N, int K, int sms, cudaStream_t stream) {
+    GB_REQUIRE(G > 0 && group_t > 0 && group_t % 256 == 0 && N > 0 && K > 0, "gb_gemm_tc_grouped: bad sizes G=%d rows=%d N=%d K=%d", G,
+               group_t, N, K);
+    GB_REQUIRE((long long)G * group_t < (1LL << 31) && (long long)G * N < (1LL << 31), "gb_gemm_tc_grouped: too many rows");
+    GB_REQUIRE(gb_gemm_tc_supported(X, ldx, W, ldw, K) && ldo % 8 == 0 && ldo >= N && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               "gb_gemm_tc_grouped: K=%d and the row pitches (%lld, %lld, %lld) must be multiples of 8 and the operands 16-byte aligned",
+               K, ldx, ldw, ldo);
+    if (ensure_status()) return 1;
+    const int T = G * group_t;
+    const long long tiles = (long long)((N + 2 * BM - 1) / (2 * BM)) * (T / 256), kb = (K + BK - 1) / BK;
+    GB_REQUIRE(tiles * kb < (1LL << 31) - (1 << 20), "gb_gemm_tc_grouped: more work than the kernel numbers");
+    TcParams p;
+    p.out = out; p.bias = nullptr; p.scratch = nullptr; p.counters = nullptr; p.status = g_status_dev;
+    p.ldo = ldo; p.out_dtype = GB_BF16; p.bias_dtype = GB_BF16; p.T = T; p.N = N; p.K = K;
+    p.swiglu = 0; p.N_out = 0; p.sms = sms;
+    p.n_ctas = 0; p.tiles = int(tiles); p.cut = CUT_WHOLE; p.per_tile = p.extra = 0;
+    p.total_its = int(tiles * kb); p.its_each = p.its_rest = 0;
+    p.row_ssq = nullptr; p.ssq_parts = 0; p.norm_size = 0; p.eps = 0.f;
+    p.resid_x = nullptr; p.resid_xb = nullptr; p.ssq_out = nullptr; p.ld_x = 0;
+    p.group_t = group_t;
+    CUtensorMap mw, mx, mo;
+    if (tensor_map_2d(W, (long long)G * N, K, ldw, BM, &mw)) return 1;
+    if (tensor_map_2d(X, T, K, ldx, 128, &mx)) return 1;
+    if (tensor_map_2d(out, T, N, ldo, 16, &mo, 128)) return 1;
+    return gemm_tc_pair_launch(mw, mx, &mo, &p, stream);
+}
+
 // Non-zero when a bounded wait inside a tensor-core kernel gave up since the last clear
 // (1: a load stage never came free, 2: a load never arrived, 3/4: an accumulator never completed or never came free).
 // Read after synchronising the stream.

@@ -53,6 +53,11 @@ struct TcParams {
     __nv_bfloat16* resid_xb;
     float* ssq_out;
     long long ld_x;
+    // several products in one launch (the kernel that pairs two SMs only): X and out hold the problems' rows one after
+    // the other, group_t rows each (a multiple of the tile's 256 tokens), W their N features each one after the other;
+    // T is the sum of all rows.  The tile whose first token is t multiplies by the features of problem t / group_t.
+    // 0: one product.
+    int group_t = 0;
 };
 
 // The work of a product is the sequence of all (tile, K block) pairs, tile after tile: tiles * kb_total

@@ -88,11 +88,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += n_pairs) {
                 const PairUnit w = pair_unit_of(u, feature_tiles, token_tiles);
+                // several products in one launch: the tile's tokens belong to one of them, whose features lie
+                // that many times N further down in W
+                const int w_first = p.group_t > 0 ? (w.t0 / p.group_t) * p.N : 0;
                 for (int kb = 0; kb < kb_total; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { atomicExch(p.status, 1); ok = false; break; }
                     if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * PSTAGE_BYTES);
                     uint8_t* a = ring + stage * PSTAGE_BYTES;
-                    tma_load_2d_pair(a, &map_w, kb * BK, w.n0 + int(rank) * BM, &full_bar[stage]);
+                    tma_load_2d_pair(a, &map_w, kb * BK, w_first + w.n0 + int(rank) * BM, &full_bar[stage]);
                     tma_load_2d_pair(a + A_BYTES, &map_x, kb * BK, w.t0 + int(rank) * PHALF, &full_bar[stage]);
                     if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
                 }

@@ -100,25 +100,27 @@ __global__ void __launch_bounds__(128) token_shift_mix_vec_kernel(const __nv_bfl
 }
 
 // h [T, E] rows ldh apart; mu [n_mix, E]; carried float32 [slots, E] (zero for a sequence that starts), read and renewed;
-// out [n_mix, T, E] of h's dtype.
+// out [n_mix, T, E] of h's dtype, the blends mix_stride elements apart (0: T * E; more where a caller pads them).
 GB_API int gb_token_shift_mix(const void* h, int dtype, long long ldh, int T, int E, const void* mu, int mu_dtype, int n_mix,
                               float* carried, const int* seq_of, const int* cu, const int* slots, const int* qlens, void* out,
-                              cudaStream_t stream) {
+                              long long mix_stride, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(mu_dtype), "gb_token_shift_mix: bad dtype");
+    if (mix_stride == 0) mix_stride = (long long)T * E;
+    GB_REQUIRE(mix_stride >= (long long)T * E, "gb_token_shift_mix: blends %lld elements apart overlap", mix_stride);
     GB_REQUIRE(E > 0 && n_mix > 0 && ldh >= E && carried, "gb_token_shift_mix: bad sizes E=%d blends=%d", E, n_mix);
     if (T == 0) return 0;
     GB_REQUIRE((E + 255) / 256 <= 65535, "gb_token_shift_mix: rows of %d entries are too long", E);
     const auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (dtype == GB_BF16 && mu_dtype == GB_BF16 && E % 8 == 0 && ldh % 8 == 0 && aligned16(h) && aligned16(mu) && aligned16(out) &&
-        aligned16(carried)) {
+        aligned16(carried) && mix_stride % 8 == 0) {
         token_shift_mix_vec_kernel<<<dim3(T, (E / 8 + 127) / 128), 128, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(h), ldh, E, static_cast<const __nv_bfloat16*>(mu), n_mix, carried, seq_of, cu, slots,
-            qlens, static_cast<__nv_bfloat16*>(out), (long long)T * E);
+            qlens, static_cast<__nv_bfloat16*>(out), mix_stride);
         GB_LAUNCH_OK("gb_token_shift_mix");
         return 0;
     }
     token_shift_mix_kernel<<<dim3(T, (E + 255) / 256), 256, 0, stream>>>(h, dtype, ldh, E, mu, mu_dtype, n_mix, carried, seq_of, cu, slots, qlens, out,
-                                                  (long long)T * E);
+                                                  mix_stride);
     GB_LAUNCH_OK("gb_token_shift_mix");
     return 0;
 }

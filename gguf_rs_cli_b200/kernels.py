@@ -190,14 +190,16 @@ def short_conv(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tens
 
 def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, carried: torch.Tensor, ctx, out: torch.Tensor) -> torch.Tensor:
     """out[s, t, :] = h[t] + (h[t-1] - h[t]) * mu[s] for every blend s; the row before a sequence's first token of the
-    step is carried [slots, E] (float32; zero when the sequence starts), which then receives the step's last row."""
+    step is carried [slots, E] (float32; zero when the sequence starts), which then receives the step's last row.
+    out [S, T', E] with T' >= T: rows from T on are left as they are."""
     _cuda(h, mu, carried, out)
     T, E = h.shape
     S = mu.shape[0]
-    assert h.stride(1) == 1 and mu.shape == (S, E) and mu.is_contiguous() and out.shape == (S, T, E) and out.is_contiguous()
+    assert h.stride(1) == 1 and mu.shape == (S, E) and mu.is_contiguous() and out.is_contiguous()
+    assert out.dim() == 3 and out.shape[0] == S and out.shape[1] >= T and out.shape[2] == E
     assert out.dtype == h.dtype and carried.dtype == torch.float32 and carried.shape[1:] == (E,) and carried.is_contiguous()
     call("gb_token_shift_mix", ptr(h), dtype_code(h), h.stride(0), T, E, ptr(mu), dtype_code(mu), S, ptr(carried), ptr(ctx.seq_of),
-         ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), stream_ptr())
+         ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), out.stride(0), stream_ptr())
     return out
 
 
@@ -766,6 +768,23 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
          GATE_ACTS[gate_activation], ptr(row_ssq),
          int(ssq_parts), int(norm_size), float(eps), ptr(resid_x), ptr(resid_xb), ptr(ssq_out),
          0 if resid_x is None else resid_x.stride(0), stream_ptr())
+    return out
+
+
+GROUPED_TILE = 256               # tokens of a tile of the kernel that pairs two SMs
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """G products of equal sizes as one launch on tcgen05: out[g] = x[g] @ w[g].T with x [G, R, K], w [G * N, K] (problem
+    g's features from row g * N on) and out [G, R, N], all bfloat16, R a multiple of GROUPED_TILE.  Rows that a caller
+    pads x with give rows of out that mean nothing.  For products too small to fill the device on their own."""
+    _cuda(x, w, out)
+    G, R, K = x.shape
+    N = out.shape[2]
+    assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and x.is_contiguous() and out.is_contiguous() and w.stride(1) == 1
+    assert w.shape == (G * N, K) and out.shape == (G, R, N) and R % GROUPED_TILE == 0
+    call("gb_gemm_tc_grouped", ptr(x), x.stride(1), ptr(w), w.stride(0), ptr(out), out.stride(1), G, R, N, K, tc_scratch(x.device).sms,
+         stream_ptr())
     return out
 
 

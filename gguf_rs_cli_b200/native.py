@@ -134,6 +134,7 @@ _SIGNATURES = {
     "gb_set_pdl": [_I],
     "gb_embed": [_P, _I, _P, _I, _I, _I, _F, _P, _P],
     "gb_embed_shadow": [_P, _I, _P, _I, _I, _I, _F, _P, _P, _P, _P],
+    "gb_gemm_tc_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "gb_gemm_tc_fused": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _L, _P],
     "gb_add_rmsnorm": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _I, _F, _P, _I, _I, _P],
     "gb_rope_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
@@ -150,7 +151,7 @@ _SIGNATURES = {
     "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P],
     "gb_short_conv": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P],
     "gb_softcap": [_P, _L, _F, _P],
-    "gb_token_shift_mix": [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "gb_token_shift_mix": [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _L, _P],
     "gb_wkv": [_P, _L, _P, _L, _P, _L, _I, _P, _I, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P],
     "gb_ssd": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
     "gb_linear_walk_scratch_floats": [_I, _I, _I, _I],

@@ -13,7 +13,9 @@ no such mixer (src/model/llama.rs has attention only).
 
 Steps of a few tokens run r, k, v, g and w1 as one product: the five blends stacked as rows against the five matrices
 stacked as columns, of whose 25 blocks the five on the diagonal are used.  Such a step is bound by reading the
-weights, which this does once and in one launch; longer steps, bound by arithmetic, run a product per blend.
+weights, which this does once and in one launch.  Long steps, bound by arithmetic, run r, k, v and g as four products
+in one launch (kernels.gemm_tc_grouped: each alone has too few tiles to fill the device), the blends padded to whole
+tiles of tokens; steps in between, and sizes that the grouped launch does not take, run a product per blend.
 
 The recurrence is the walk that gated linear attention uses, reading the state before the token's own update
 (csrc/wkv.cu, csrc/gla.cu).  Decays, their exponentials, the bonus and the state are 32-bit.
@@ -33,6 +35,7 @@ from .registry import register_mixer
 
 BLENDS = ("r", "k", "v", "g", "w")
 STACK_MAX_TOKENS = 24            # 5 * 24 rows: still one tile of tokens for the tensor-core product
+GROUPED_MIN_TOKENS = 512         # from here on, and where padding to whole tiles adds at most an eighth, one grouped launch
 
 
 @register_mixer("wkv")
@@ -95,17 +98,26 @@ class TimeMix(Part):
 
     def forward(self, h, ctx: StepContext, run: RunView) -> torch.Tensor:
         H, D, T = self.H, self.D, h.shape[0]
-        blends = ctx.ws.get("wkv.blends", (len(BLENDS), T, self.E), ctx.dtype)
+        n = H * D
+        padded = -(-T // kernels.GROUPED_TILE) * kernels.GROUPED_TILE
+        grouped = (self.stack is not None and n % 8 == 0 and T >= GROUPED_MIN_TOKENS and (padded - T) * 8 <= T
+                   and all(self.off[s] == i * n for i, s in enumerate(("r", "k", "v", "g"))))
+        rows = padded if grouped else T
+        blends = ctx.ws.get("wkv.blends", (len(BLENDS), rows, self.E), ctx.dtype)
         kernels.token_shift_mix(h, self.mu, ctx.state(f"run{run.index}.prev"), ctx, blends)
         ctx.mark("shift")
-        n = H * D
-        if self.stack is not None and T <= STACK_MAX_TOKENS:
+        if grouped:
+            both = ctx.ws.get("wkv.rkvg", (4, rows, n), ctx.dtype)
+            kernels.gemm_tc_grouped(blends[:4], self.stack.weight[:4 * n], both)
+            r, k, v, g = (both[i, :T] for i in range(4))
+            low = self.w1(blends[4, :T], ctx, activation="tanh")
+        elif self.stack is not None and T <= STACK_MAX_TOKENS:
             both = self.stack(blends.view(len(BLENDS) * T, self.E), ctx)
             r, k, v, g = (both[i * T:(i + 1) * T, self.off[s]:self.off[s] + n] for i, s in enumerate(("r", "k", "v", "g")))
             low = kernels.unary_act_(both[4 * T:5 * T, self.off["w1"]:self.off["w1"] + self.rank], "tanh")
         else:
-            r, k, v, g = (self.proj[s](blends[i], ctx) for i, s in enumerate(("r", "k", "v", "g")))
-            low = self.w1(blends[4], ctx, activation="tanh")
+            r, k, v, g = (self.proj[s](blends[i, :T], ctx) for i, s in enumerate(("r", "k", "v", "g")))
+            low = self.w1(blends[4, :T], ctx, activation="tanh")
         # the decay's second product keeps 32-bit results: their exponentials enter the recurrence
         a = self.w2(low, ctx, out_dtype=torch.float32)
         ctx.mark("projections")

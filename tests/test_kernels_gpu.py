@@ -134,6 +134,26 @@ def test_gemm_tensor_core(T, N, Kd, out_dtype):
     assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("G,R,N,Kd", [(1, 256, 256, 64), (4, 512, 256, 328), (3, 768, 328, 136), (5, 256, 40, 72), (2, 1024, 1000, 512)])
+def test_gemm_tensor_core_grouped(G, R, N, Kd):
+    """Several products in one launch: every problem against its own plain product, rows of the next problem untouched
+    by a tile that reaches beyond the features (N no multiple of a tile), and as close to the single launch as rounding."""
+    k = K()
+    g = torch.Generator().manual_seed(G + R + N + Kd)
+    x = torch.randn(G, R, Kd, generator=g).to(BF).to(DEV)
+    w = (torch.randn(G * N, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    out = torch.full((G, R, N), float("nan"), dtype=BF, device=DEV)
+    k.gemm_tc_grouped(x, w, out)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    for i in range(G):
+        want = P.linear(x[i].double().cpu(), w[i * N:(i + 1) * N].double().cpu(), None)
+        assert rel_err(out[i], want) < 5e-3, f"problem {i}"
+        alone = torch.empty(R, N, dtype=BF, device=DEV)
+        k.gemm_tc(x[i], w[i * N:(i + 1) * N], None, alone)
+        assert rel_err(out[i], alone.double().cpu()) < 5e-3, f"problem {i} differs from its own launch"
+
+
 def test_gemm_tensor_core_refuses_what_it_cannot_take():
     k = K()
     x = torch.zeros(4, 100, dtype=BF, device=DEV)

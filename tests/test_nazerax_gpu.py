@@ -270,6 +270,25 @@ def test_whole_request_alone(name, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("n", [700, 1000])
+def test_long_prompt_whose_wkv_projections_run_as_one_launch(n):
+    """A prompt long enough for the grouped product of r, k, v and g (its blends padded to whole tiles of tokens), alone and
+    beside a short one, and then cut so that the same positions come from products of their own."""
+    eng = new_engine("wide", "bfloat16")
+    toks, want = tokens_of("wide", n, 9), plain_logits("wide", n, 9)
+    rows = list(range(0, n, 37)) + [n - 1]
+    s, s2 = eng.open(), eng.open()
+    got = eng.step([entry(s2, toks[:5], ()), entry(s, toks, rows)])
+    assert_close(got, want[rows], "bfloat16", f"prompt of {n}")
+    eng.close(s), eng.close(s2)
+    s = eng.open()
+    eng.step([entry(s, toks[:300], ())])
+    cut = eng.step([entry(s, toks[300:], [r - 300 for r in rows if r >= 300])])
+    assert_close(cut, want[[r for r in rows if r >= 300]], "bfloat16", f"prompt of {n} in two portions")
+    eng.close(s)
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_stream_after_every_layer_run(name, dtype):
