@@ -35,6 +35,9 @@ class LayerSpec:
     feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     position: Optional[PartSpec] = None
+    # further parts that the block arrangement wires in by name (kinds of the registry of extra parts), for instance
+    # an input of the layer's own that depends on the token alone
+    extras: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -40,6 +40,8 @@ struct AdParams {
     long long ldg;
     int gate_per_head;           // the gate is [T, nh]: one number for all entries of a head's result
     int sink;                    // the softmax's denominator counts one more key of score 0 that has no value
+    const float* sink_values;    // ... or of the score sink_values[head] (not scaled); null: 0
+    int chunk;                   // > 0: in a window's place, a token sees the earlier tokens of its own chunk of that many positions
 };
 
 __device__ __forceinline__ float ad_gated(const AdParams& p, int t, int h, int d, float o) {
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
     __syncthreads();
 
     const int pos = p.pos[t];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = gb_first_visible(pos, p.window, p.chunk);
     // the pages of the window, and in front of them those pages of kept first positions that the window does not reach
     const int keep = p.window > 0 ? p.keep_first : 0;
     const int first_page = lo >> GB_PAGE_SHIFT;
@@ -217,7 +219,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             o += acc_s[w][gi][d] * wgt;
         }
         if (p.splits == 1) {
-            if (p.sink && M != -INFINITY) L += exp2f(-M);
+            if (p.sink && M != -INFINITY) L += exp2f((p.sink_values ? p.sink_values[h0 + gi] * 1.4426950408889634f : 0.f) - M);
             p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
         } else {
             float* rec = p.scratch + ((size_t(t) * p.nh + h0 + gi) * p.splits + split) * (hd + 2);
@@ -246,7 +248,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             L += __ldcg(rec + s * (hd + 2) + hd + 1) * wgt;
             o += __ldcg(rec + s * (hd + 2) + d) * wgt;
         }
-        if (p.sink && M != -INFINITY) L += exp2f(-M);
+        if (p.sink && M != -INFINITY) L += exp2f((p.sink_values ? p.sink_values[h0 + gi] * 1.4426950408889634f : 0.f) - M);
         p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
     }
     if (threadIdx.x == 0) p.counters[t * gridDim.y + ytile] = 0;
@@ -283,7 +285,9 @@ static int attention_decode_launch(const void* q, long long ldq, void* out, long
                                    const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
                                    const void* kcache, const void* vcache, int window, float scale, int splits,
                                    float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
-                                   const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
+                                   const void* gate, long long ldg, int gate_per_head, int sink, const float* sink_values, int chunk,
+                                   cudaStream_t stream) {
+    GB_REQUIRE(chunk >= 0 && (chunk == 0 || (window == 0 && keep_first == 0)), "gb_attention_decode: chunks go with neither a window nor kept positions");
     GB_REQUIRE(gb_attention_decode_supported(hd, GB_BF16, GB_BF16), "gb_attention_decode: head_dim %d must be a multiple of 16 up to 256", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_decode: %d heads are not a multiple of %d KV heads", nh, nkv);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && splits >= 1 && head_pages >= 0, "gb_attention_decode: bad cache geometry");
@@ -301,7 +305,7 @@ static int attention_decode_launch(const void* q, long long ldq, void* out, long
     p.counters = counters; p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.hd = hd; p.table_width = table_width;
     p.ring_pages = ring_pages; p.window = window; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
     p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
-    p.gate_per_head = gate_per_head; p.sink = sink;
+    p.gate_per_head = gate_per_head; p.sink = sink; p.sink_values = sink_values; p.chunk = chunk;
     dim3 grid(T, nkv * gtiles, splits);
     int hc = (hd + 63) / 64;
     switch (gt) {
@@ -319,18 +323,20 @@ GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long lon
                                const void* kcache, const void* vcache, int window, float scale, int splits,
                                float* scratch, int* counters, int n_counters, cudaStream_t stream) {
     return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
-                                   window, scale, splits, scratch, counters, n_counters, 0, 0, nullptr, 0, 0, 0, stream);
+                                   window, scale, splits, scratch, counters, n_counters, 0, 0, nullptr, 0, 0, 0, nullptr, 0, stream);
 }
 
 // The same behind a window that keeps the sequence's first keep_first positions visible (their pages are the first
 // head_pages entries of the page table), the result multiplied by sigmoid(gate) when a gate [T, nh*hd] (gate_per_head:
-// [T, nh]) is given; sink: one more key of score 0 without a value in the softmax's denominator.
+// [T, nh]) is given; sink: one more key without a value in the softmax's denominator, of score 0 or sink_values[head];
+// chunk: in a window's place, chunks of that many positions counted from the sequence's start.
 GB_API int gb_attention_decode_kept(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
                                     const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
                                     const void* kcache, const void* vcache, int window, float scale, int splits,
                                     float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
-                                    const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
+                                    const void* gate, long long ldg, int gate_per_head, int sink, const float* sink_values,
+                                    int chunk, cudaStream_t stream) {
     return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
                                    window, scale, splits, scratch, counters, n_counters, head_pages, keep_first, gate, ldg,
-                                   gate_per_head, sink, stream);
+                                   gate_per_head, sink, sink_values, chunk, stream);
 }

@@ -11,7 +11,9 @@
 // keep_first positions of a sequence stay visible behind the window (their pages are the
 // first head_pages entries of the page table, in front of the ring); the result is
 // multiplied by sigmoid(gate) entry by entry, or by one number per head; the softmax's denominator may count one
-// more key of score 0 that has no value (a sink).
+// more key that has no value (a sink), of score 0 or of a learned score per head (not scaled).  Instead of a window
+// the keys may come in chunks of `chunk` positions counted from the sequence's start: a token sees the earlier tokens of
+// its own chunk only.
 #include <math.h>
 
 #include "common.cuh"
@@ -28,7 +30,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     int nh, int nkv, int hd, int hdv, int v_row, const int* __restrict__ seq_of, const int* __restrict__ pos,
     const int* __restrict__ table, int table_width, int ring_pages, const TC* __restrict__ kc,
     const TC* __restrict__ vc, int window, float scale, int head_pages, int keep_first, const void* __restrict__ gate,
-    int gate_dtype, long long ldg, int gate_per_head, int sink) {
+    int gate_dtype, long long ldg, int gate_per_head, int sink, const float* __restrict__ sink_values, int chunk) {
     int t = blockIdx.x, h = blockIdx.y;
     int b = seq_of[t];
     size_t orow = size_t(t) * ldo + size_t(h) * hdv;
@@ -44,7 +46,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
 
     int p = pos[t];
     const bool vec8 = hd % 8 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;     // key rows start on 16 bytes
-    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    int lo = gb_first_visible(p, window, chunk);
     int g = h / (nh / nkv);
     const int* trow = table + size_t(b) * table_width;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -162,11 +164,20 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
-    if (sink && M != -INFINITY) L += expf(-M);
+    float down = 1.f;                    // a sink above every score: the sums are brought down to its level
+    if (sink && M != -INFINITY) {
+        const float sv = sink_values ? sink_values[h] : 0.f;
+        if (sv > M) {
+            down = expf(M - sv);
+            L = L * down + 1.f;
+        } else {
+            L += expf(sv - M);
+        }
+    }
     for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < AG_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        o /= L;
+        o = o * down / L;
         if (gate) o *= 1.f / (1.f + expf(-gb_load(gate, gate_dtype, size_t(t) * ldg + (gate_per_head ? size_t(h) : size_t(h) * hdv + d))));
         gb_store(out, out_dtype, orow + d, o);
     }
@@ -181,7 +192,7 @@ GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void*
                                 const int* table, int table_width, int ring_pages, const void* kcache,
                                 const void* vcache, int cache_dtype, int window, float scale, int head_pages, int keep_first,
                                 const void* gate, int gate_dtype, long long ldg, int gate_per_head, int sink,
-                                cudaStream_t stream) {
+                                const float* sink_values, int chunk, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(q_dtype) && gb_is_dtype(out_dtype) && gb_is_dtype(cache_dtype), "gb_attention_generic: bad dtype");
     GB_REQUIRE(hd > 0 && hd <= AG_MAX_HD, "gb_attention_generic: head_dim %d is not in 1..%d", hd, AG_MAX_HD);
     GB_REQUIRE(hdv > 0 && hdv <= AG_MAX_HD && v_row >= hdv, "gb_attention_generic: value size %d (rows of %d) is not in 1..%d", hdv, v_row, AG_MAX_HD);
@@ -189,13 +200,14 @@ GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void*
     GB_REQUIRE(nh <= 65535, "gb_attention_generic: too many heads (%d)", nh);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && head_pages >= 0, "gb_attention_generic: bad cache geometry");
     GB_REQUIRE(keep_first >= 0, "gb_attention_generic: a negative number of kept positions");
+    GB_REQUIRE(chunk >= 0 && (chunk == 0 || (window == 0 && keep_first == 0)), "gb_attention_generic: chunks go with neither a window nor kept positions");
     GB_REQUIRE(!gate || gb_is_dtype(gate_dtype), "gb_attention_generic: bad gate dtype");
     if (T == 0) return 0;
     dim3 grid(T, nh);
 #define AG_LAUNCH(TC, MAX_HD)                                                                                     \
     attention_generic_kernel<TC, MAX_HD><<<grid, AG_WARPS * 32, 0, stream>>>(                                     \
         q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, hdv, v_row, seq_of, pos, table, table_width, ring_pages, \
-        (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg, gate_per_head, sink)
+        (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg, gate_per_head, sink, sink_values, chunk)
     const bool small = hd <= 256 && hdv <= 256;
     if (cache_dtype == GB_F32) {
         if (small) AG_LAUNCH(float, 256);

@@ -47,6 +47,8 @@ struct ApParams {
     long long ldg;
     int gate_per_head;               // the gate is [T, nh]: one number for all entries of a head's result
     int sink;                        // the softmax's denominator counts one more key of score 0 that has no value
+    const float* sink_values;        // ... or of the score sink_values[head] (not scaled); null: 0
+    int chunk;                       // > 0: in a window's place, a token sees the earlier tokens of its own chunk of that many positions
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
 
     // key pages this tile needs
     const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
-    const int kb_begin = p.window > 0 ? max(0, pos_lo - p.window + 1) >> GB_PAGE_SHIFT : 0;
+    const int kb_begin = gb_first_visible(pos_lo, p.window, p.chunk) >> GB_PAGE_SHIFT;
     const int kb_end = (pos_hi >> GB_PAGE_SHIFT) + 1;
     // pages in front of the window that hold kept first positions come first in the walk
     const int keep = p.window > 0 ? p.keep_first : 0;
@@ -145,7 +147,7 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     // this thread's two query rows and their positions (-1: no such query)
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
     const int pq0 = r0 < rows ? start + q0 + r0 : -1, pq1 = r1 < rows ? start + q0 + r1 : -1;
-    const int lo0 = p.window > 0 ? pq0 - p.window + 1 : 0, lo1 = p.window > 0 ? pq1 - p.window + 1 : 0;
+    const int lo0 = gb_first_visible(pq0, p.window, p.chunk), lo1 = gb_first_visible(pq1, p.window, p.chunk);
 
     float o[OT][4];
 #pragma unroll
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
         }
         // ---- mask and online softmax (two rows per thread: r0 in c0,c1 and r1 in c2,c3)
         const int key0 = kb * AP_BN + 2 * (lane & 3);
-        const bool need_mask = (kb * AP_BN + AP_BN - 1 > pos_lo) || (p.window > 0);
+        const bool need_mask = (kb * AP_BN + AP_BN - 1 > pos_lo) || (p.window > 0) || (p.chunk > 0);
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
@@ -272,8 +274,9 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     if (p.sink) {
-        if (m0 != -INFINITY) l0 += exp2f(-m0 * p.scale_log2);
-        if (m1 != -INFINITY) l1 += exp2f(-m1 * p.scale_log2);
+        const float sv = p.sink_values ? p.sink_values[h] * 1.4426950408889634f : 0.f;
+        if (m0 != -INFINITY) l0 += exp2f(sv - m0 * p.scale_log2);
+        if (m1 != -INFINITY) l1 += exp2f(sv - m1 * p.scale_log2);
     }
     float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
     const bool entry_gate = p.gate && !p.gate_per_head;
@@ -332,7 +335,8 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
                                 const int* tiles, int n_tiles, const int* cu, const int* starts, const int* qlens,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
                                 const void* vcache, int window, float scale, int exact, int head_pages, int keep_first,
-                                const void* gate, long long ldg, int gate_per_head, int sink, cudaStream_t stream) {
+                                const void* gate, long long ldg, int gate_per_head, int sink, const float* sink_values, int chunk,
+                                cudaStream_t stream) {
     GB_REQUIRE(gb_attention_prefill_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill: head_dim %d is not 64 or 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
     GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill: %d tiles of queries are too many for one launch", n_tiles);
@@ -349,7 +353,7 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
     p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width; p.ring_pages = ring_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
-    p.gate_per_head = gate_per_head; p.sink = sink;
+    p.gate_per_head = gate_per_head; p.sink = sink; p.sink_values = sink_values; p.chunk = chunk;
     if (exact) return hd == 64 ? launch_ap<64, true>(p, n_tiles, stream) : launch_ap<128, true>(p, n_tiles, stream);
     return hd == 64 ? launch_ap<64, false>(p, n_tiles, stream) : launch_ap<128, false>(p, n_tiles, stream);
 }

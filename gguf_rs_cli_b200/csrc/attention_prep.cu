@@ -82,15 +82,15 @@ GB_API int gb_qk_norm_kv_write(void* q, const void* k, const void* v, int dtype,
 // this step's rows, when given).  q [H, D + Rd]: the last Rd entries of each head are rotated likewise and
 // written to qa, head h's part starting at entry h * qa_stride + qa_off of the token's row (qa may be q
 // itself: the rotation is then done in place).
-// Rotation: the first rot_dims entries of the part, pair (2i, 2i+1) by position * inv_freq[i]; the rest
-// pass unchanged.
+// Rotation: the first rot_dims entries of the part, pair (2i, 2i+1) by position * inv_freq[i], or with `halves` pair
+// (i, i + rot_dims/2); the rest pass unchanged.
 __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, const void* __restrict__ dkv,
                                    long long ldd, int dtype, int H, int D, int Rd, int C, int rot_dims,
                                    const float* __restrict__ inv_freq, const void* __restrict__ w, int w_dtype, float eps,
                                    void* qa, long long lda, int qa_stride, int qa_off, void* __restrict__ row_out,
                                    const int* __restrict__ seq_of,
                                    const int* __restrict__ pos, const int* __restrict__ table, int table_width,
-                                   int ring_pages, void* __restrict__ cache, int cache_dtype) {
+                                   int ring_pages, void* __restrict__ cache, int cache_dtype, int halves) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int b = seq_of[t];
@@ -121,27 +121,30 @@ __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, co
         const int item = idx / pairs, i = idx - item * pairs;
         float sn = 0.f, cs = 1.f;
         if (i < half) sincosf(float(p) * inv_freq[i], &sn, &cs);
+        // the pair that angle i turns: neighbours (2i, 2i+1), or with `halves` entries (i, i + half); pairs behind the
+        // rotated entries pass unchanged either way
+        const int d0 = halves && i < half ? i : 2 * i, d1 = halves && i < half ? i + half : 2 * i + 1;
         float x0, x1, y0, y1;
         if (item == 0) {
-            x0 = gb_load(dkv, dtype, drow + C + 2 * i);
-            x1 = gb_load(dkv, dtype, drow + C + 2 * i + 1);
+            x0 = gb_load(dkv, dtype, drow + C + d0);
+            x1 = gb_load(dkv, dtype, drow + C + d1);
         } else {
-            const size_t o = size_t(t) * ldq + size_t(item - 1) * (D + Rd) + D + 2 * i;
-            x0 = gb_load(q, dtype, o);
-            x1 = gb_load(q, dtype, o + 1);
+            const size_t o = size_t(t) * ldq + size_t(item - 1) * (D + Rd) + D;
+            x0 = gb_load(q, dtype, o + d0);
+            x1 = gb_load(q, dtype, o + d1);
         }
         gb_rotate(x0, x1, cs, sn, y0, y1);
         if (item == 0) {
-            gb_store(cache, cache_dtype, crow + C + 2 * i, y0);
-            gb_store(cache, cache_dtype, crow + C + 2 * i + 1, y1);
+            gb_store(cache, cache_dtype, crow + C + d0, y0);
+            gb_store(cache, cache_dtype, crow + C + d1, y1);
             if (row_out) {
-                gb_store(row_out, dtype, rrow + C + 2 * i, y0);
-                gb_store(row_out, dtype, rrow + C + 2 * i + 1, y1);
+                gb_store(row_out, dtype, rrow + C + d0, y0);
+                gb_store(row_out, dtype, rrow + C + d1, y1);
             }
         } else {
-            const size_t o = size_t(t) * lda + size_t(item - 1) * qa_stride + qa_off + 2 * i;
-            gb_store(qa, dtype, o, y0);
-            gb_store(qa, dtype, o + 1, y1);
+            const size_t o = size_t(t) * lda + size_t(item - 1) * qa_stride + qa_off;
+            gb_store(qa, dtype, o + d0, y0);
+            gb_store(qa, dtype, o + d1, y1);
         }
     }
 }
@@ -149,7 +152,7 @@ __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, co
 GB_API int gb_latent_prep(const void* q, long long ldq, const void* dkv, long long ldd, int dtype, int T, int H, int D, int Rd,
                           int C, int rot_dims, const float* inv_freq, const void* w, int w_dtype, float eps, void* qa,
                           long long lda, int qa_stride, int qa_off, void* row_out, const int* seq_of, const int* pos,
-                          const int* table, int table_width, int ring_pages, void* cache, int cache_dtype,
+                          const int* table, int table_width, int ring_pages, void* cache, int cache_dtype, int halves,
                           cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(cache_dtype), "gb_latent_prep: bad dtype");
     GB_REQUIRE(H > 0 && D >= 0 && C > 0 && Rd >= 0 && Rd % 2 == 0 && rot_dims >= 0 && rot_dims <= Rd && rot_dims % 2 == 0,
@@ -158,7 +161,7 @@ GB_API int gb_latent_prep(const void* q, long long ldq, const void* dkv, long lo
     GB_REQUIRE(table && cache && ring_pages > 0 && table_width >= 1 && eps > 0.f, "gb_latent_prep: cache missing");
     if (T == 0) return 0;
     latent_prep_kernel<<<T, 128, 0, stream>>>(q, ldq, dkv, ldd, dtype, H, D, Rd, C, rot_dims, inv_freq, w, w_dtype, eps, qa, lda,
-                                              qa_stride, qa_off, row_out, seq_of, pos, table, table_width, ring_pages, cache, cache_dtype);
+                                              qa_stride, qa_off, row_out, seq_of, pos, table, table_width, ring_pages, cache, cache_dtype, halves);
     GB_LAUNCH_OK("gb_latent_prep");
     return 0;
 }
@@ -315,7 +318,8 @@ __global__ void __launch_bounds__(128) head_prep_kv_write_kernel(const HeadPrepP
     const size_t row = size_t(t) * size_t(a.ld);
     const int* trow = a.table + size_t(b) * a.table_width;
     const int half = a.inv_freq ? a.rot_dims / 2 : 0;
-    for (int item = warp; item < H + 2 * G; item += warps) {
+    const int items = a.k ? H + 2 * G : H;          // a layer that reads another layer's keys and values prepares its queries only
+    for (int item = warp; item < items; item += warps) {
         if (item < H + G) {
             const bool is_q = item < H;
             const void* src = is_q ? (const void*)a.q : a.k;
@@ -371,7 +375,8 @@ GB_API int gb_head_prep_kv_write(void* q, const void* k, const void* v, int dtyp
     GB_REQUIRE(H > 0 && G > 0 && D > 0 && Dv > 0 && D <= 4096, "gb_head_prep_kv_write: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d", H, G, D, Dv);
     GB_REQUIRE((wq == nullptr) == (wk == nullptr) && (!wq || (gb_is_dtype(w_dtype) && eps > 0.f)), "gb_head_prep_kv_write: bad norm");
     GB_REQUIRE(!inv_freq || (rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= D), "gb_head_prep_kv_write: %d of %d entries cannot be rotated", rot_dims, D);
-    GB_REQUIRE(q && k && v && table && kcache && vcache && ring_pages > 0 && head_pages >= 0 && table_width >= 1, "gb_head_prep_kv_write: arguments missing");
+    GB_REQUIRE(q && table && ring_pages > 0 && head_pages >= 0 && table_width >= 1, "gb_head_prep_kv_write: arguments missing");
+    GB_REQUIRE((k && v && kcache && vcache) || (!k && !v), "gb_head_prep_kv_write: keys and values come together with their caches, or not at all");
     if (T == 0) return 0;
     HeadPrepParams a;
     a.q = q; a.k = k; a.v = v; a.ld = ld; a.dtype = dtype; a.H = H; a.G = G; a.D = D; a.Dv = Dv; a.wq = wq; a.wk = wk;

@@ -98,6 +98,13 @@ __device__ __forceinline__ size_t gb_kv_offset(const int* row, int ring_pages, i
     return ((size_t(page) * nkv + g) * GB_PAGE + (pos & (GB_PAGE - 1))) * size_t(hd);
 }
 
+// The first position that position p sees: behind a window of `window` positions p - window + 1; with chunks of `chunk`
+// positions counted from the sequence's start, the first position of p's own chunk; else 0.
+__device__ __forceinline__ int gb_first_visible(int p, int window, int chunk) {
+    if (chunk > 0) return (p / chunk) * chunk;
+    return window > 0 ? max(0, p - window + 1) : 0;
+}
+
 // Rotation of one pair by the angle whose sine and cosine are given.  Products and sums are rounded one by
 // one (no fused multiply-add), so that every kernel that rotates gives the same bits.
 __device__ __forceinline__ void gb_rotate(float x0, float x1, float cs, float sn, float& y0, float& y1) {

@@ -2,10 +2,13 @@
 // CUDA cores with 32-bit sums, token by token (steps of few tokens, the 32-bit mode, and sizes the tiled kernel of
 // moe_grouped.cu does not take).
 //
-// Choice (one warp per token, all 32-bit): s_e = sigmoid(z_e).  The experts form n_groups equal groups of
-// neighbours; a group's mark is the sum of its two largest s (of its one, if it has one expert); only experts of
-// the `keep` groups with the largest marks can be chosen; of those the `top` with the largest s are, and their
-// weights are s / (sum of the chosen s + 1e-20) * scale.  Equal values: the lower index wins.
+// Choice (one warp per token, all 32-bit): s_e = sigmoid(z_e), or softmax(z)_e over all experts.  The experts form
+// n_groups equal groups of neighbours; a group's mark is the sum of its two largest choice scores (of its one, if it has
+// one expert); only experts of the `keep` groups with the largest marks can be chosen; of those the `top` with the
+// largest choice scores are, and their weights are s / (sum of the chosen s + 1e-20) * scale.  The choice score is s, or
+// s plus a correction per expert that the weights do not see.  Equal values: the lower index wins.
+//
+// Identity experts: the experts numbered n_real and above have no matrices; what they give is the token's own row.
 #include <math.h>
 
 #include "common.cuh"
@@ -23,25 +26,34 @@ static int moe_smem(const void* kernel, size_t bytes, const char* what) {
 
 // The choice for one token by one warp; z: the token's logits (shared or global memory).
 __device__ void moe_route_warp(const float* z, int E, int n_groups, int keep, int top, float scale, int* __restrict__ ids,
-                               float* __restrict__ weights, float* s, float* mark, unsigned char* open_, int* chosen, int lane) {
+                               float* __restrict__ weights, float* s, float* c, float* mark, unsigned char* open_, int* chosen,
+                               int lane, int softmax, const float* __restrict__ corr) {
     const int size = E / n_groups;
+    float zmax = -INFINITY, zsum = 0.f;
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = gb_warp_max(zmax);
+        for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
+        zsum = gb_warp_sum(zsum);
+    }
     for (int e = lane; e < E; e += 32) {
-        s[e] = 1.f / (1.f + expf(-z[e]));
+        s[e] = softmax ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+        c[e] = corr ? s[e] + corr[e] : s[e];
         open_[e] = 0;
     }
     __syncwarp();
     for (int g = lane; g < n_groups; g += 32) {
-        float a = -1.f, b = -1.f;                           // the two largest (scores are positive)
+        float a = -INFINITY, b = -INFINITY;                 // the two largest
         for (int i = 0; i < size; ++i) {
-            const float v = s[g * size + i];
+            const float v = c[g * size + i];
             if (v > a) { b = a; a = v; }
             else if (v > b) b = v;
         }
-        mark[g] = a + (b > 0.f ? b : 0.f);
+        mark[g] = a + (b > -INFINITY ? b : 0.f);
     }
     __syncwarp();
     for (int r = 0; r < keep; ++r) {                        // the group with the largest mark, `keep` times
-        float best = -1.f;
+        float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int g = lane; g < n_groups; g += 32)
             if (mark[g] > best) { best = mark[g]; arg = g; }
@@ -52,16 +64,16 @@ __device__ void moe_route_warp(const float* z, int E, int n_groups, int keep, in
         }
         if (arg != 0x7fffffff) {
             for (int i = lane; i < size; i += 32) open_[arg * size + i] = 1;
-            if (lane == 0) mark[arg] = -2.f;
+            if (lane == 0) mark[arg] = -INFINITY;
         }
         __syncwarp();
     }
     float sum = 0.f;
     for (int r = 0; r < top; ++r) {
-        float best = -1.f;
+        float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32)
-            if (open_[e] && s[e] > best) { best = s[e]; arg = e; }
+            if (open_[e] && c[e] > best) { best = c[e]; arg = e; }
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
@@ -71,8 +83,8 @@ __device__ void moe_route_warp(const float* z, int E, int n_groups, int keep, in
             chosen[r] = arg == 0x7fffffff ? 0 : arg;
             if (arg != 0x7fffffff) open_[arg] = 0;
         }
-        sum += arg == 0x7fffffff ? 0.f : best;
         __syncwarp();
+        sum += arg == 0x7fffffff ? 0.f : s[arg];
     }
     for (int r = lane; r < top; r += 32) {
         ids[r] = chosen[r];
@@ -81,24 +93,27 @@ __device__ void moe_route_warp(const float* z, int E, int n_groups, int keep, in
 }
 
 __global__ void __launch_bounds__(32) moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int top,
-                                                       float scale, int* __restrict__ ids, float* __restrict__ weights) {
+                                                       float scale, int* __restrict__ ids, float* __restrict__ weights,
+                                                       int softmax, const float* __restrict__ corr) {
     __shared__ float s[MOE_MAX_EXPERTS];
+    __shared__ float c[MOE_MAX_EXPERTS];
     __shared__ float mark[MOE_MAX_EXPERTS];
     __shared__ unsigned char open_[MOE_MAX_EXPERTS];        // 1: the expert may still be chosen
     __shared__ int chosen[MOE_MAX_TOP];
     const int t = blockIdx.x;
-    moe_route_warp(z + size_t(t) * E, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, mark,
-                   open_, chosen, threadIdx.x);
+    moe_route_warp(z + size_t(t) * E, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, c, mark,
+                   open_, chosen, threadIdx.x, softmax, corr);
 }
 
 // z float32 [T, E] router logits -> ids int32 [T, top], weights float32 [T, top], largest score first.
+// softmax: the scores are softmax(z) instead of sigmoids; corr [E] float32 or null: added to the scores for the choice only.
 GB_API int gb_moe_route(const float* z, int T, int E, int n_groups, int keep, int top, float scale, int* ids, float* weights,
-                        cudaStream_t stream) {
+                        int softmax, const float* corr, cudaStream_t stream) {
     GB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS, "gb_moe_route: %d experts (1..%d)", E, MOE_MAX_EXPERTS);
     GB_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups, "gb_moe_route: %d experts in %d groups, %d kept", E, n_groups, keep);
     GB_REQUIRE(top > 0 && top <= MOE_MAX_TOP && top <= keep * (E / n_groups), "gb_moe_route: %d experts cannot be chosen from %d groups of %d (at most %d)", top, keep, E / n_groups, MOE_MAX_TOP);
     if (T == 0) return 0;
-    moe_route_kernel<<<T, 32, 0, stream>>>(z, E, n_groups, keep, top, scale, ids, weights);
+    moe_route_kernel<<<T, 32, 0, stream>>>(z, E, n_groups, keep, top, scale, ids, weights, softmax, corr);
     GB_LAUNCH_OK("gb_moe_route");
     return 0;
 }
@@ -111,10 +126,12 @@ __device__ __forceinline__ float moe_row_dot(const TW* __restrict__ w, const flo
 template <typename TW>
 __global__ void __launch_bounds__(256) moe_router_kernel(const void* __restrict__ x, int x_dtype, long long ldx, int K,
                                                          const TW* __restrict__ w, int E, int n_groups, int keep, int top,
-                                                         float scale, int* __restrict__ ids, float* __restrict__ weights) {
+                                                         float scale, int* __restrict__ ids, float* __restrict__ weights,
+                                                         int softmax, const float* __restrict__ corr) {
     extern __shared__ float moe_xs[];
     __shared__ float z[MOE_MAX_EXPERTS];
     __shared__ float s[MOE_MAX_EXPERTS];
+    __shared__ float c[MOE_MAX_EXPERTS];
     __shared__ float mark[MOE_MAX_EXPERTS];
     __shared__ unsigned char open_[MOE_MAX_EXPERTS];
     __shared__ int chosen[MOE_MAX_TOP];
@@ -127,7 +144,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const void* __restrict_
     }
     __syncthreads();
     if (warp == 0)
-        moe_route_warp(z, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, mark, open_, chosen, lane);
+        moe_route_warp(z, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, c, mark, open_, chosen,
+                       lane, softmax, corr);
 }
 
 // ---------------------------------------------------------------- experts, token by token
@@ -180,10 +198,11 @@ template <typename TW>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const void* __restrict__ h, int h_dtype, long long ldh, int K, int F,
                                                           int top, const int* __restrict__ ids, const TW* __restrict__ wg,
                                                           const TW* __restrict__ wu, float limit, void* __restrict__ y,
-                                                          int y_dtype) {
+                                                          int y_dtype, int n_real) {
     extern __shared__ float moe_hs[];
     const int pair = blockIdx.x, t = pair / top;
     const int e = ids[pair];
+    if (e >= n_real) return;                       // an identity expert has no unit
     for (int i = threadIdx.x; i < K; i += blockDim.x) moe_hs[i] = gb_load(h, h_dtype, size_t(t) * ldh + i);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -205,10 +224,17 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const void* __restrict
 template <typename TW>
 __global__ void __launch_bounds__(128) moe_down_kernel(const void* __restrict__ y, int y_dtype, int F, int N,
                                                        const int* __restrict__ ids, const TW* __restrict__ wd,
-                                                       float* __restrict__ z) {
+                                                       float* __restrict__ z, int n_real, const void* __restrict__ h,
+                                                       int h_dtype, long long ldh, int top) {
     extern __shared__ float moe_ys[];
     const int pair = blockIdx.x;
     const int e = ids[pair];
+    if (e >= n_real) {                             // an identity expert: the pair's row is the token's own row
+        const int n_end = min(N, (blockIdx.y + 1) * MOE_SLICE);
+        for (int n = blockIdx.y * MOE_SLICE + threadIdx.x; n < n_end; n += blockDim.x)
+            z[size_t(pair) * N + n] = gb_load(h, h_dtype, size_t(pair / top) * ldh + n);
+        return;
+    }
     for (int i = threadIdx.x; i < F; i += blockDim.x) moe_ys[i] = gb_load(y, y_dtype, size_t(pair) * F + i);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -232,7 +258,8 @@ __global__ void moe_pair_sum_kernel(const float* __restrict__ z, const float* __
 
 // x [T, K] rows ldx apart (the rows the router reads, 32-bit where the caller has them); w [E, K] contiguous.
 GB_API int gb_moe_router(const void* x, int x_dtype, long long ldx, int T, int K, const void* w, int w_dtype, int E, int n_groups,
-                         int keep, int top, float scale, int* ids, float* weights, cudaStream_t stream) {
+                         int keep, int top, float scale, int* ids, float* weights, int softmax, const float* corr,
+                         cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(x_dtype) && gb_is_dtype(w_dtype), "gb_moe_router: bad dtype");
     GB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && K > 0, "gb_moe_router: %d experts (1..%d)", E, MOE_MAX_EXPERTS);
     GB_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups, "gb_moe_router: %d experts in %d groups, %d kept", E, n_groups, keep);
@@ -240,11 +267,11 @@ GB_API int gb_moe_router(const void* x, int x_dtype, long long ldx, int T, int K
     if (T == 0) return 0;
     const size_t smem = size_t(K) * 4;
     if (w_dtype == GB_F32) {
-        if (moe_smem((const void*)moe_router_kernel<float>, smem + 16 * 1024, "gb_moe_router")) return 1;
-        moe_router_kernel<float><<<T, 256, smem, stream>>>(x, x_dtype, ldx, K, (const float*)w, E, n_groups, keep, top, scale, ids, weights);
+        if (moe_smem((const void*)moe_router_kernel<float>, smem + 20 * 1024, "gb_moe_router")) return 1;
+        moe_router_kernel<float><<<T, 256, smem, stream>>>(x, x_dtype, ldx, K, (const float*)w, E, n_groups, keep, top, scale, ids, weights, softmax, corr);
     } else {
-        if (moe_smem((const void*)moe_router_kernel<__nv_bfloat16>, smem + 16 * 1024, "gb_moe_router")) return 1;
-        moe_router_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>(x, x_dtype, ldx, K, (const __nv_bfloat16*)w, E, n_groups, keep, top, scale, ids, weights);
+        if (moe_smem((const void*)moe_router_kernel<__nv_bfloat16>, smem + 20 * 1024, "gb_moe_router")) return 1;
+        moe_router_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>(x, x_dtype, ldx, K, (const __nv_bfloat16*)w, E, n_groups, keep, top, scale, ids, weights, softmax, corr);
     }
     GB_LAUNCH_OK("gb_moe_router");
     return 0;
@@ -252,7 +279,8 @@ GB_API int gb_moe_router(const void* x, int x_dtype, long long ldx, int T, int K
 
 // h [T, K] rows ldh apart; ids [T, top]; wg, wu [E, F, K] contiguous (dtype w_dtype); y [T, top, F] contiguous.
 GB_API int gb_moe_gate_up(const void* h, int h_dtype, long long ldh, int T, int K, int F, int top, const int* ids,
-                          const void* wg, const void* wu, int w_dtype, float limit, void* y, int y_dtype, cudaStream_t stream) {
+                          const void* wg, const void* wu, int w_dtype, float limit, void* y, int y_dtype, int n_real,
+                          cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(h_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(y_dtype), "gb_moe_gate_up: bad dtype");
     GB_REQUIRE(K > 0 && F > 0 && top > 0 && limit > 0.f, "gb_moe_gate_up: bad sizes K=%d F=%d top=%d limit=%g", K, F, top, limit);
     if (T == 0) return 0;
@@ -261,20 +289,23 @@ GB_API int gb_moe_gate_up(const void* h, int h_dtype, long long ldh, int T, int 
     GB_REQUIRE(grid.y <= 65535, "gb_moe_gate_up: an expert of %d hidden entries is too wide", F);
     if (w_dtype == GB_F32) {
         if (moe_smem((const void*)moe_gate_up_kernel<float>, smem, "gb_moe_gate_up")) return 1;
-        moe_gate_up_kernel<float><<<grid, 128, smem, stream>>>(h, h_dtype, ldh, K, F, top, ids, (const float*)wg, (const float*)wu, limit, y, y_dtype);
+        moe_gate_up_kernel<float><<<grid, 128, smem, stream>>>(h, h_dtype, ldh, K, F, top, ids, (const float*)wg, (const float*)wu, limit, y, y_dtype, n_real);
     } else {
         if (moe_smem((const void*)moe_gate_up_kernel<__nv_bfloat16>, smem, "gb_moe_gate_up")) return 1;
         moe_gate_up_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(h, h_dtype, ldh, K, F, top, ids, (const __nv_bfloat16*)wg,
-                                                                        (const __nv_bfloat16*)wu, limit, y, y_dtype);
+                                                                        (const __nv_bfloat16*)wu, limit, y, y_dtype, n_real);
     }
     GB_LAUNCH_OK("gb_moe_gate_up");
     return 0;
 }
 
 // y [T, top, F]; wd [E, N, F] contiguous; z float32 [T * top, N] scratch; out float32 [T, N] contiguous (added to when
-// accumulate).  Two launches.
+// accumulate).  Experts numbered n_real and above are identity experts: their pairs' rows are the tokens' own rows h
+// [T, N] (rows ldh apart).  Two launches.
 GB_API int gb_moe_down(const void* y, int y_dtype, int T, int F, int N, int top, const int* ids, const float* weights,
-                       const void* wd, int w_dtype, float* z, float* out, int accumulate, cudaStream_t stream) {
+                       const void* wd, int w_dtype, float* z, float* out, int accumulate, int n_real, const void* h, int h_dtype,
+                       long long ldh, cudaStream_t stream) {
+    GB_REQUIRE(n_real > 0 && (!h || gb_is_dtype(h_dtype)), "gb_moe_down: bad identity arguments");
     GB_REQUIRE(gb_is_dtype(y_dtype) && gb_is_dtype(w_dtype), "gb_moe_down: bad dtype");
     GB_REQUIRE(F > 0 && N > 0 && top > 0 && z, "gb_moe_down: bad sizes F=%d N=%d top=%d", F, N, top);
     if (T == 0) return 0;
@@ -283,10 +314,10 @@ GB_API int gb_moe_down(const void* y, int y_dtype, int T, int F, int N, int top,
     GB_REQUIRE(grid.y <= 65535, "gb_moe_down: rows of %d entries are too wide", N);
     if (w_dtype == GB_F32) {
         if (moe_smem((const void*)moe_down_kernel<float>, smem, "gb_moe_down")) return 1;
-        moe_down_kernel<float><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, ids, (const float*)wd, z);
+        moe_down_kernel<float><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, ids, (const float*)wd, z, h ? n_real : 0x7fffffff, h, h_dtype, ldh, top);
     } else {
         if (moe_smem((const void*)moe_down_kernel<__nv_bfloat16>, smem, "gb_moe_down")) return 1;
-        moe_down_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, ids, (const __nv_bfloat16*)wd, z);
+        moe_down_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, ids, (const __nv_bfloat16*)wd, z, h ? n_real : 0x7fffffff, h, h_dtype, ldh, top);
     }
     GB_LAUNCH_OK("gb_moe_down");
     const long long total = (long long)T * N;

@@ -41,6 +41,14 @@ __device__ __forceinline__ int mg_swz(int row, int chunk) { return row * MG_BK +
 
 }  // namespace
 
+// What an identity expert gives for a pair: the token's own row.
+struct MoeIdentity {
+    const int* ids;                 // [T, top]; null: no identity experts
+    const void* h;                  // [T, N] rows ldh apart
+    long long ldh;
+    int n_real, h_dtype;
+};
+
 // ids [n_pairs] -> offsets [E + 1], perm [n_pairs] (pairs in the order of their experts), tiles [max_tiles][2] = (expert,
 // first place in perm), n_tiles [1].  Places inside an expert's range are handed out by atomics on shared memory: their
 // order is not fixed, and nothing depends on it (every pair's rows are computed for themselves).
@@ -91,13 +99,16 @@ __global__ void moe_gather_rows_kernel(const uint4* __restrict__ h, long long ld
 // out[t, n] (+)= sum_r weights[t, r] z[place_of[t * top + r], n], the choices in their order.
 __global__ void moe_combine_sorted_kernel(const float* __restrict__ z, const int* __restrict__ place_of,
                                           const float* __restrict__ weights, int top, int N, float* __restrict__ out, int accumulate,
-                                          long long total) {
+                                          long long total, const MoeIdentity id) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / N;
     const int n = int(i - t * N);
     float acc = 0.f;
-    for (int r = 0; r < top; ++r) acc = fmaf(weights[t * top + r], z[size_t(place_of[t * top + r]) * N + n], acc);
+    for (int r = 0; r < top; ++r) {
+        const bool own = id.ids && id.ids[t * top + r] >= id.n_real;
+        acc = fmaf(weights[t * top + r], own ? gb_load(id.h, id.h_dtype, size_t(t) * id.ldh + n) : z[size_t(place_of[t * top + r]) * N + n], acc);
+    }
     out[i] = accumulate ? out[i] + acc : acc;
 }
 
@@ -109,7 +120,9 @@ struct MgParams {
     long long lda;
     int a_div, N, K;
     float limit;
+    int n_real;                     // experts numbered n_real and above have no matrices (identity experts): their tiles are left out
 };
+
 
 template <bool GLU>
 __global__ void __launch_bounds__(MG_THREADS, 5) moe_grouped_kernel(const MgParams p) {
@@ -122,6 +135,7 @@ __global__ void __launch_bounds__(MG_THREADS, 5) moe_grouped_kernel(const MgPara
     // CTAs that run together share a tile's gathered rows and walk through one expert's matrix
     if (int(blockIdx.y) >= p.n_tiles[0]) return;
     const int e = p.tiles[2 * blockIdx.y], place0 = p.tiles[2 * blockIdx.y + 1];
+    if (e >= p.n_real) return;
     const int n_rows = min(MG_BM, p.offsets[e + 1] - place0);
     const int n0 = blockIdx.x * MG_BN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -230,13 +244,16 @@ __global__ void __launch_bounds__(MG_THREADS, 5) moe_grouped_kernel(const MgPara
 
 // out[t, n] (+)= sum_r weights[t, r] z[t * top + r, n], the choices in their order.
 __global__ void moe_combine_kernel(const float* __restrict__ z, const float* __restrict__ weights, int top, int N,
-                                   float* __restrict__ out, int accumulate, long long total) {
+                                   float* __restrict__ out, int accumulate, long long total, const MoeIdentity id) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / N;
     const int n = int(i - t * N);
     float acc = 0.f;
-    for (int r = 0; r < top; ++r) acc = fmaf(weights[t * top + r], z[(t * top + r) * N + n], acc);
+    for (int r = 0; r < top; ++r) {
+        const bool own = id.ids && id.ids[t * top + r] >= id.n_real;
+        acc = fmaf(weights[t * top + r], own ? gb_load(id.h, id.h_dtype, size_t(t) * id.ldh + n) : z[(t * top + r) * N + n], acc);
+    }
     out[i] = accumulate ? out[i] + acc : acc;
 }
 
@@ -249,10 +266,12 @@ GB_API long long gb_moe_grouped_scratch_ints(int T, int top, int E) {
 }
 
 // h bfloat16 [T, K] rows ldh apart; ids [T, top], weights [T, top]; wg, wu [E, F, K], wd [E, N, F] bfloat16 contiguous;
-// y bfloat16 [T*top, F], z float [T*top, N] scratch; out float [T, N] (added to when accumulate).
+// y bfloat16 [T*top, F], z float [T*top, N] scratch; out float [T, N] (added to when accumulate).  E counts all experts
+// that ids may name; those numbered n_real and above are identity experts without matrices (then N = K).
 GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int N, int E, int top, const int* ids,
                           const float* weights, const void* wg, const void* wu, const void* wd, float limit, void* y, float* z,
-                          int* scratch, float* out, int accumulate, cudaStream_t stream) {
+                          int* scratch, float* out, int accumulate, int n_real, cudaStream_t stream) {
+    GB_REQUIRE(n_real > 0 && n_real <= E && (n_real == E || N == K), "gb_moe_grouped: %d of %d experts have matrices (rows of %d and %d)", n_real, E, K, N);
     GB_REQUIRE(gb_moe_grouped_supported(K, F), "gb_moe_grouped: sizes K=%d F=%d must be multiples of 8", K, F);
     GB_REQUIRE(E > 0 && E <= 1024 && top > 0 && N > 0 && limit > 0.f && (ldh % 8) == 0, "gb_moe_grouped: bad sizes");
     GB_REQUIRE(((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu) |
@@ -277,7 +296,7 @@ GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int
     MgParams p;
     p.a = (const __nv_bfloat16*)h; p.w0 = (const __nv_bfloat16*)wg; p.w1 = (const __nv_bfloat16*)wu; p.out = y;
     p.offsets = offsets; p.perm = perm; p.tiles = tiles; p.n_tiles = n_tiles; p.lda = ldh; p.a_div = top; p.N = F; p.K = K;
-    p.limit = limit;
+    p.limit = limit; p.n_real = n_real;
     moe_grouped_kernel<true><<<dim3((F + MG_BN - 1) / MG_BN, max_tiles), MG_THREADS, SMEM_GLU, stream>>>(p);
     GB_LAUNCH_OK("gb_moe_grouped (gate, up)");
     p.a = (const __nv_bfloat16*)y; p.w0 = (const __nv_bfloat16*)wd; p.w1 = nullptr; p.out = z; p.lda = F; p.a_div = 1;
@@ -285,7 +304,9 @@ GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int
     moe_grouped_kernel<false><<<dim3((N + MG_BN - 1) / MG_BN, max_tiles), MG_THREADS, SMEM_ONE, stream>>>(p);
     GB_LAUNCH_OK("gb_moe_grouped (down)");
     const long long total = (long long)T * N;
-    moe_combine_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, weights, top, N, out, accumulate, total);
+    MoeIdentity id;
+    id.ids = n_real < E ? ids : nullptr; id.h = h; id.ldh = ldh; id.n_real = n_real; id.h_dtype = GB_BF16;
+    moe_combine_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, weights, top, N, out, accumulate, total, id);
     GB_LAUNCH_OK("gb_moe_grouped (sum)");
     return 0;
 }
@@ -313,11 +334,16 @@ GB_API int gb_moe_gather_rows(const void* h, long long ldh, int T, int K, int to
     return 0;
 }
 
+// ids, n_real, h (rows ldh apart): pairs whose expert is numbered n_real or above take the token's row of h instead of a
+// row of z (ids null: none do).
 GB_API int gb_moe_combine_sorted(const float* z, const int* place_of, const float* weights, int T, int top, int N, float* out,
-                                 int accumulate, cudaStream_t stream) {
+                                 int accumulate, const int* ids, int n_real, const void* h, int h_dtype, long long ldh,
+                                 cudaStream_t stream) {
     if (T == 0) return 0;
+    MoeIdentity id;
+    id.ids = ids; id.h = h; id.ldh = ldh; id.n_real = n_real; id.h_dtype = h_dtype;
     const long long total = (long long)T * N;
-    moe_combine_sorted_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, place_of, weights, top, N, out, accumulate, total);
+    moe_combine_sorted_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, place_of, weights, top, N, out, accumulate, total, id);
     GB_LAUNCH_OK("gb_moe_combine_sorted");
     return 0;
 }

@@ -79,16 +79,19 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
                       seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                       kcache: torch.Tensor, vcache: Optional[torch.Tensor], window: int, scale: float,
                       v_dim: Optional[int] = None, keep_first: int = 0, head_pages: int = 0,
-                      gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, sink: bool = False, sink_values: Optional[torch.Tensor] = None,
+                      chunk: int = 0) -> torch.Tensor:
     """v_dim: entries of a value when they differ from a key's head_dim.  vcache None: the values are the
     first v_dim entries of the key rows themselves (one latent row per position serves as key and value).
     keep_first: with a window, the sequence's first positions that stay visible behind it; their pages are the first
     head_pages entries of the page table, in front of the ring.  gate [T, heads*v_dim]: the result is multiplied by
     sigmoid(gate); a gate [T, heads] holds one number per head.  sink: the softmax's denominator counts one more key
-    of score 0 that has no value."""
-    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
+    of score 0 that has no value, or of the score sink_values[head] (float32 [heads], not scaled).  chunk: instead of a
+    window, a token sees the earlier tokens of its own chunk of that many positions, counted from the sequence's start."""
+    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate, sink_values)
     T = q.shape[0]
     per_head = _gate_per_head(gate, out, n_heads)
+    assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads and sink_values.is_contiguous())
     v_dim = head_dim if v_dim is None else int(v_dim)
     v_row = head_dim if vcache is None else vcache.shape[-1]
     assert kcache.shape[-1] == head_dim and v_row >= v_dim and (vcache is None or vcache.dtype == kcache.dtype)
@@ -97,7 +100,8 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
          n_heads, n_kv_heads, head_dim, v_dim, v_row, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages,
          ptr(kcache), ptr(kcache if vcache is None else vcache), dtype_code(kcache), int(window or 0), float(scale),
          int(head_pages), int(keep_first or 0), ptr(gate), 0 if gate is None else dtype_code(gate),
-         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
+         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink) or sink_values is not None), ptr(sink_values),
+         int(chunk or 0), stream_ptr())
     return out
 
 
@@ -388,7 +392,7 @@ def norm_residual_add(x: torch.Tensor, y: Optional[torch.Tensor], weight: Option
          ptr(weight), 0 if weight is None else dtype_code(weight), float(eps), ptr(xb), stream_ptr())
 
 
-def head_prep_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+def head_prep_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        inv_freq: Optional[torch.Tensor], rotary_dim: int, pairing: int, v_first: Optional[torch.Tensor],
                        mix: float, first_out: Optional[torch.Tensor], seq_of: torch.Tensor, pos: torch.Tensor,
@@ -399,8 +403,12 @@ def head_prep_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_head
     into the cache; first_out receives v as it came."""
     _cuda(q, k, v, q_weight, k_weight, inv_freq, v_first, first_out, seq_of, pos, table, kcache, vcache)
     T, ld = q.shape[0], q.stride(0)
-    assert q.stride(1) == 1 and k.stride(0) == ld and v.stride(0) == ld and k.dtype == q.dtype == v.dtype
-    assert kcache.shape[-1] == dim and vcache.shape[-1] == vdim and kcache.dtype == vcache.dtype
+    if k is None:                       # a layer that reads another layer's keys and values: its queries only
+        assert v is None and v_first is None and first_out is None
+        kcache = vcache = None
+    else:
+        assert q.stride(1) == 1 and k.stride(0) == ld and v.stride(0) == ld and k.dtype == q.dtype == v.dtype
+        assert kcache.shape[-1] == dim and vcache.shape[-1] == vdim and kcache.dtype == vcache.dtype
     assert (q_weight is None) == (k_weight is None) and (q_weight is None or (q_weight.numel() == dim == k_weight.numel() and q_weight.dtype == k_weight.dtype))
     for t in (v_first, first_out):
         assert t is None or (t.shape == (T, n_kv_heads * vdim) and t.stride(1) == 1 and t.dtype == q.dtype)
@@ -408,11 +416,11 @@ def head_prep_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_head
          ptr(k_weight), 0 if q_weight is None else dtype_code(q_weight), float(eps), ptr(inv_freq), int(rotary_dim), int(pairing),
          ptr(v_first), 0 if v_first is None else v_first.stride(0), float(mix), ptr(first_out),
          0 if first_out is None else first_out.stride(0), ptr(seq_of), ptr(pos), ptr(table), table.shape[1], int(ring_pages),
-         int(head_pages), ptr(kcache), ptr(vcache), dtype_code(kcache), stream_ptr())
+         int(head_pages), ptr(kcache), ptr(vcache), 0 if kcache is None else dtype_code(kcache), stream_ptr())
 
 
 def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, scale: float, ids: torch.Tensor,
-              weights: torch.Tensor) -> None:
+              weights: torch.Tensor, softmax: bool = False, correction: Optional[torch.Tensor] = None) -> None:
     """Router logits float32 [T, experts] -> ids int32 [T, top] and weights float32 [T, top]: scores are sigmoids; the
     experts form n_groups equal groups of neighbours, a group's mark is the sum of its two largest scores, only the
     `keep` best groups' experts can be chosen; weights are the chosen scores over their sum, times scale."""
@@ -420,22 +428,32 @@ def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, scale: f
     T, E = logits.shape
     assert logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32
     assert ids.shape == (T, top) and weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
-    call("gb_moe_route", ptr(logits), T, E, int(n_groups), int(keep), int(top), float(scale), ptr(ids), ptr(weights), stream_ptr())
+    _check_correction(correction, E)
+    call("gb_moe_route", ptr(logits), T, E, int(n_groups), int(keep), int(top), float(scale), ptr(ids), ptr(weights),
+         int(bool(softmax)), ptr(correction), stream_ptr())
+
+
+def _check_correction(correction: Optional[torch.Tensor], n: int) -> None:
+    assert correction is None or (correction.is_cuda and correction.dtype == torch.float32 and correction.numel() == n
+                                  and correction.is_contiguous())
 
 
 def moe_router(x: torch.Tensor, w: torch.Tensor, n_groups: int, keep: int, top: int, scale: float, ids: torch.Tensor,
-               weights: torch.Tensor) -> None:
-    """The router's product x w^T (32-bit sums) and the choice of moe_route in one kernel; x [T, K], w [experts, K]."""
+               weights: torch.Tensor, softmax: bool = False, correction: Optional[torch.Tensor] = None) -> None:
+    """The router's product x w^T (32-bit sums) and the choice of moe_route in one kernel; x [T, K], w [experts, K].
+    softmax: scores are softmax over all experts instead of sigmoids; correction float32 [experts]: added to the scores
+    for the choice, not for the weights."""
     _cuda(x, w, ids, weights)
     T, K = x.shape
     assert x.stride(1) == 1 and w.is_contiguous() and w.shape[1] == K and ids.dtype == torch.int32 and weights.dtype == torch.float32
     assert ids.shape == (T, top) and weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
+    _check_correction(correction, w.shape[0])
     call("gb_moe_router", ptr(x), dtype_code(x), x.stride(0), T, K, ptr(w), dtype_code(w), w.shape[0], int(n_groups), int(keep),
-         int(top), float(scale), ptr(ids), ptr(weights), stream_ptr())
+         int(top), float(scale), ptr(ids), ptr(weights), int(bool(softmax)), ptr(correction), stream_ptr())
 
 
 def moe_gate_up(h: torch.Tensor, ids: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, limit: float,
-                y: torch.Tensor) -> torch.Tensor:
+                y: torch.Tensor, identity: int = 0) -> torch.Tensor:
     """y[t, r, :] = unit(W_gate[e] h_t, W_up[e] h_t), e = ids[t, r]; unit(g, u) = g' sigmoid(1.702 g') (u' + 1) with
     g' = min(g, limit), u' = clamp(u, -limit, limit).  w_gate, w_up [experts, F, K]; token by token on the CUDA cores."""
     _cuda(h, ids, w_gate, w_up, y)
@@ -445,12 +463,12 @@ def moe_gate_up(h: torch.Tensor, ids: torch.Tensor, w_gate: torch.Tensor, w_up: 
     assert h.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_gate.shape == w_up.shape == (E, F, K)
     assert w_gate.dtype == w_up.dtype and y.shape == (T, top, F) and y.is_contiguous() and ids.is_contiguous()
     call("gb_moe_gate_up", ptr(h), dtype_code(h), h.stride(0), T, K, F, top, ptr(ids), ptr(w_gate), ptr(w_up), dtype_code(w_gate),
-         float(limit), ptr(y), dtype_code(y), stream_ptr())
+         float(limit), ptr(y), dtype_code(y), E if identity else 0x7fffffff, stream_ptr())
     return y
 
 
 def moe_down(y: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor,
-             accumulate: bool = False, ws=None) -> torch.Tensor:
+             accumulate: bool = False, ws=None, identity: int = 0, h: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] (+)= sum_r weights[t, r] W_down[ids[t, r]] y[t, r]; w_down [experts, N, F]; out float32 [T, N].  Every pair's
     row first (32-bit, in a buffer of the workspace `ws` when given), then the weighted sum per token: two launches."""
     _cuda(y, ids, weights, w_down, out)
@@ -459,8 +477,12 @@ def moe_down(y: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_down: 
     assert y.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, N, F) and out.shape == (T, N)
     assert out.dtype == torch.float32 and out.is_contiguous() and ids.shape == (T, top) and weights.shape == (T, top)
     z = ws.get("moe.rows", (T * top, N), torch.float32) if ws is not None else torch.empty(T * top, N, dtype=torch.float32, device=y.device)
+    # identity experts (ids from the number of matrices on, `identity` of them) give the token's own row h [T, N]
+    assert not identity or (h is not None and h.shape == (T, N) and h.stride(1) == 1)
+    own = h if identity else None
     call("gb_moe_down", ptr(y), dtype_code(y), T, F, N, top, ptr(ids), ptr(weights), ptr(w_down), dtype_code(w_down), ptr(z),
-         ptr(out), int(bool(accumulate)), stream_ptr())
+         ptr(out), int(bool(accumulate)), E, ptr(own), 0 if own is None else dtype_code(own), 0 if own is None else own.stride(0),
+         stream_ptr())
     return out
 
 
@@ -471,7 +493,7 @@ def moe_grouped_supported(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
 
 
 def moe_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False) -> torch.Tensor:
+                w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False, identity: int = 0) -> torch.Tensor:
     """The routed experts of a step of many tokens on the tensor cores: the (token, choice) pairs sorted by expert on
     the device, gate and up with the clamped unit, down, and the weighted sum per token; what moe_gate_up and moe_down
     give, up to the rounding of bfloat16 unit outputs.  Four launches."""
@@ -484,14 +506,15 @@ def moe_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     assert ids.shape == weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
     y = ctx.ws.get("moe.units", (T, top, F), torch.bfloat16)
     z = ctx.ws.get("moe.rows", (T * top, N), torch.float32)
-    scratch = ctx.ws.get("moe.sorted", (native.library().gb_moe_grouped_scratch_ints(T, top, E),), torch.int32)
-    call("gb_moe_grouped", ptr(h), h.stride(0), T, K, F, N, E, top, ptr(ids), ptr(weights), ptr(w_gate), ptr(w_up), ptr(w_down),
-         float(limit), ptr(y), ptr(z), ptr(scratch), ptr(out), int(bool(accumulate)), stream_ptr())
+    n_all = E + int(identity)                 # identity experts are numbered behind those with matrices
+    scratch = ctx.ws.get("moe.sorted", (native.library().gb_moe_grouped_scratch_ints(T, top, n_all),), torch.int32)
+    call("gb_moe_grouped", ptr(h), h.stride(0), T, K, F, N, n_all, top, ptr(ids), ptr(weights), ptr(w_gate), ptr(w_up), ptr(w_down),
+         float(limit), ptr(y), ptr(z), ptr(scratch), ptr(out), int(bool(accumulate)), E, stream_ptr())
     return out
 
 
 def moe_by_expert(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                  w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False) -> torch.Tensor:
+                  w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False, identity: int = 0) -> torch.Tensor:
     """The routed experts of a step of very many tokens as ordinary products, expert by expert, on the tcgen05 product
     kernels: the pairs sorted by expert and the tokens' rows gathered in that order on the device; the experts' offsets
     read on the host (one wait per call: such steps are prompts, which no graph captures); per expert gate, up and down
@@ -503,10 +526,11 @@ def moe_by_expert(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_g
     P = T * top
     assert h.dtype == torch.bfloat16 and w_gate.dtype == torch.bfloat16 and out.dtype == torch.float32 and out.shape == (T, N)
     lib = native.library()
-    scratch = ctx.ws.get("moe.sorted", (lib.gb_moe_grouped_scratch_ints(T, top, E),), torch.int32)
-    order = ctx.ws.get("moe.order", (E + 1 + 2 * P,), torch.int32)
-    offsets, perm, place_of = order[:E + 1], order[E + 1:E + 1 + P], order[E + 1 + P:]
-    call("gb_moe_sort", ptr(ids), T, top, E, ptr(offsets), ptr(perm), ptr(place_of), ptr(scratch), stream_ptr())
+    n_all = E + int(identity)                 # identity experts are sorted behind the others; their rows are never multiplied
+    scratch = ctx.ws.get("moe.sorted", (lib.gb_moe_grouped_scratch_ints(T, top, n_all),), torch.int32)
+    order = ctx.ws.get("moe.order", (n_all + 1 + 2 * P,), torch.int32)
+    offsets, perm, place_of = order[:n_all + 1], order[n_all + 1:n_all + 1 + P], order[n_all + 1 + P:]
+    call("gb_moe_sort", ptr(ids), T, top, n_all, ptr(offsets), ptr(perm), ptr(place_of), ptr(scratch), stream_ptr())
     rows = ctx.ws.get("moe.gathered", (P, K), torch.bfloat16)
     call("gb_moe_gather_rows", ptr(h), h.stride(0), T, K, top, ptr(perm), ptr(rows), stream_ptr())
     at = offsets.cpu().tolist()
@@ -522,7 +546,8 @@ def moe_by_expert(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_g
         a, b = at[e], at[e + 1]
         if b > a:
             gemm(y[a:b], w_down[e], None, z[a:b])
-    call("gb_moe_combine_sorted", ptr(z), ptr(place_of), ptr(weights), T, top, N, ptr(out), int(bool(accumulate)), stream_ptr())
+    call("gb_moe_combine_sorted", ptr(z), ptr(place_of), ptr(weights), T, top, N, ptr(out), int(bool(accumulate)),
+         ptr(ids) if identity else None, E, ptr(h), dtype_code(h), h.stride(0), stream_ptr())
     return out
 
 
@@ -571,7 +596,7 @@ def qk_norm_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, n_heads: int, dim: int, rot_dim: int, kv_rank: int, rot_dims: int,
                 inv_freq: Optional[torch.Tensor], weight: torch.Tensor, eps: float, qa: Optional[torch.Tensor],
                 seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int, cache: torch.Tensor,
-                row_out: Optional[torch.Tensor] = None) -> None:
+                row_out: Optional[torch.Tensor] = None, halves: bool = False) -> None:
     """Latent attention in front of the attention kernel: dkv [T, kv_rank + rot_dim] gives the cache row
     (RMS-normed latent, rotated shared key part; also copied to row_out [T, kv_rank + rot_dim] when given); the
     heads' rotated query parts go to qa [T, heads*(kv_rank + rot_dim)] behind the kv_rank entries that
@@ -589,7 +614,8 @@ def latent_prep(q: torch.Tensor, dkv: torch.Tensor, n_heads: int, dim: int, rot_
     assert row_out is None or (row_out.shape == (T, kv_rank + rot_dim) and row_out.is_contiguous() and row_out.dtype == q.dtype)
     call("gb_latent_prep", ptr(q), q.stride(0), ptr(dkv), dkv.stride(0), dtype_code(q), T, n_heads, dim, rot_dim, kv_rank,
          rot_dims, ptr(inv_freq), ptr(weight), dtype_code(weight), float(eps), ptr(qa), qa.stride(0), stride, off,
-         ptr(row_out), ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(cache), dtype_code(cache), stream_ptr())
+         ptr(row_out), ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(cache), dtype_code(cache),
+         int(bool(halves)), stream_ptr())
 
 
 def pack_latent_heads(kv: torch.Tensor, row: torch.Tensor, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
@@ -644,6 +670,71 @@ def head_matmul(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch
     assert x.shape[1] >= (H - 1) * x_head_stride + I and out.shape[1] >= (H - 1) * out_head_stride + O
     call("gb_head_matmul", ptr(x), dtype_code(x), x.stride(0), int(x_head_stride), ptr(w), dtype_code(w), H, I, O, ptr(out),
          dtype_code(out), out.stride(0), int(out_head_stride), T, stream_ptr())
+    return out
+
+
+def selective_scan(x: torch.Tensor, z: torch.Tensor, low: torch.Tensor, dt_rank: int, n_state: int, dt: torch.Tensor,
+                   dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                   ctx) -> torch.Tensor:
+    """The selective scan per channel c and state entry n, from and into state [slots, inner, n_state] (float32):
+    dt' = softplus(dt + dt_bias); S[c, n] <- exp(-exp(a_log[c, n]) dt'_c) S[c, n] + dt'_c x_c B_n; y_c = sum_n S[c, n] C_n +
+    skip_c x_c; out = y * silu(z).  x, z [T, inner]; low float32 [T, dt_rank + 2 n_state] holds B and C behind its first
+    dt_rank columns; dt float32 [T, inner]; dt_bias, skip [inner], a_log [inner, n_state] float32.  Prompts of more
+    than 256 tokens run in segments of 128 side by side (three launches)."""
+    _cuda(x, z, low, dt, dt_bias, a_log, skip, state, out)
+    T, inner = x.shape
+    assert z.shape == (T, inner) and x.dtype == z.dtype and x.stride(1) == 1 and z.stride(1) == 1
+    assert low.dtype == torch.float32 and low.shape == (T, dt_rank + 2 * n_state) and low.stride(1) == 1
+    assert dt.dtype == torch.float32 and dt.shape == (T, inner) and dt.stride(1) == 1
+    for t, shape in ((dt_bias, (inner,)), (a_log, (inner, n_state)), (skip, (inner,))):
+        assert t.dtype == torch.float32 and t.shape == shape and t.is_contiguous()
+    assert state.dtype == torch.float32 and state.shape[1:] == (inner, n_state) and state.is_contiguous()
+    assert out.shape == (T, inner) and out.stride(1) == 1
+    n = native.library().gb_selective_scan_segment_floats(ctx.B, int(ctx.max_qlen), inner, n_state)
+    seg = ctx.ws.get("scan.segments", (n,), torch.float32) if n else None
+    call("gb_selective_scan", ptr(x), x.stride(0), ptr(z), z.stride(0), dtype_code(x), ptr(low), low.stride(0), int(dt_rank),
+         int(n_state), ptr(dt), dt.stride(0), ptr(dt_bias), ptr(a_log), ptr(skip), ptr(state), ptr(out), out.stride(0),
+         dtype_code(out), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), T, ctx.B, inner, int(ctx.max_qlen), ptr(seg), stream_ptr())
+    if seg is not None:
+        native.count_launches(2)
+    return out
+
+
+def norm_sandwich(x: Optional[torch.Tensor], y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                  y2: Optional[torch.Tensor] = None, inner_weights=None, mix: float = 1.0,
+                  next_weight: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None,
+                  xb: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None) -> None:
+    """One pass over each row for a layer that norms what a sublayer reads and what it gives (rms(v) = sqrt(mean(v^2) +
+    eps), 32-bit sums): u = y, or with y2 u = mix (y / rms(y) wy + y2 / rms(y2) wy2) for inner_weights (wy, wy2);
+    x += u / rms(u) weight (x float32 [T, E]); then, each optional, h = x / rms(x) next_weight (the rows the next sublayer
+    reads) and xb = bfloat16(x).  weight None: u itself goes to u_out (float32) and x is not touched.  y None: only h and xb."""
+    wy, wy2 = inner_weights if inner_weights is not None else (None, None)
+    _cuda(x, y, y2, weight, wy, wy2, next_weight, h, xb, u_out)
+    ref = x if x is not None else y
+    T, E = ref.shape
+    ws = [w for w in (weight, wy, wy2, next_weight) if w is not None]
+    assert ws and all(w.dtype == ws[0].dtype and w.numel() == E and w.is_contiguous() for w in ws)
+    assert x is None or (x.dtype == torch.float32 and x.is_contiguous())
+    for t in (y, y2):
+        assert t is None or (t.shape == (T, E) and t.stride(1) == 1)
+    assert h is None or (h.shape == (T, E) and h.is_contiguous())
+    assert xb is None or (xb.dtype == torch.bfloat16 and xb.shape == (T, E) and xb.is_contiguous())
+    assert u_out is None or (u_out.dtype == torch.float32 and u_out.shape == (T, E) and u_out.is_contiguous())
+    call("gb_norm_sandwich", ptr(x), ptr(y), 0 if y is None else dtype_code(y), 0 if y is None else y.stride(0), ptr(y2),
+         0 if y2 is None else dtype_code(y2), 0 if y2 is None else y2.stride(0), ptr(wy), ptr(wy2), float(mix), ptr(weight),
+         ptr(next_weight), dtype_code(ws[0]), float(eps), ptr(h), 0 if h is None else dtype_code(h), ptr(xb), ptr(u_out), T, E,
+         stream_ptr())
+
+
+def token_side_gate(a: torch.Tensor, table: torch.Tensor, offset: int, tokens: torch.Tensor, out: torch.Tensor,
+                    activation: str = "gelu_tanh") -> torch.Tensor:
+    """out[t, j] = act(a[t, j]) * table[token_t, offset + j] for the dim = a.shape[1] columns of a layer's slice of a
+    per-token table [vocabulary, all layers' columns]."""
+    _cuda(a, table, tokens, out)
+    T, dim = a.shape
+    assert a.stride(1) == 1 and table.stride(1) == 1 and out.shape == (T, dim) and out.stride(1) == 1 and tokens.numel() == T
+    call("gb_token_side_gate", ptr(a), dtype_code(a), a.stride(0), ptr(table), dtype_code(table), table.stride(0), int(offset),
+         ptr(tokens), table.shape[0], T, dim, GATE_ACTS[activation], ptr(out), dtype_code(out), out.stride(0), stream_ptr())
     return out
 
 
@@ -860,16 +951,19 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
                      splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None,
                      rope: Optional[tuple] = None, keep_first: int = 0, head_pages: int = 0,
-                     gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, sink: bool = False, sink_values: Optional[torch.Tensor] = None,
+                     chunk: int = 0) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
     the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
     where it fits) or the CUDA-core one (any head size that is a multiple of 16).
     rope = (k, v, inv_freq, rotary_dim, pairing), tensor-core kernel only: q, k and v are the
     unrotated projections; the kernel rotates q and k and writes k and v into the cache itself
     (k and v None: it reads another run's cache and only rotates q).
-    keep_first, head_pages, gate, sink (CUDA-core kernel only): as attention_generic."""
-    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
-    kept = bool(keep_first or head_pages or gate is not None or sink)
+    keep_first, head_pages, gate, sink, sink_values, chunk (CUDA-core kernel only): as attention_generic."""
+    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate, sink_values)
+    assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads and sink_values.is_contiguous())
+    sink = bool(sink) or sink_values is not None
+    kept = bool(keep_first or head_pages or gate is not None or sink or chunk)
     assert not kept or (mma is False and rope is None)
     assert gate is None or gate.dtype == torch.bfloat16
     per_head = _gate_per_head(gate, out, n_heads)
@@ -902,7 +996,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
         call("gb_attention_decode_kept", ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
              ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
              float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), int(head_pages),
-             int(keep_first or 0), ptr(gate), 0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
+             int(keep_first or 0), ptr(gate), 0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)),
+             ptr(sink_values), int(chunk or 0), stream_ptr())
         return out
     call(entry, ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
          ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
@@ -936,18 +1031,21 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
                       tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
                       scale: float, tc: Optional[bool] = None, exact: bool = False, keep_first: int = 0, head_pages: int = 0,
-                      gate: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, sink: bool = False, sink_values: Optional[torch.Tensor] = None,
+                      chunk: int = 0) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
     values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (the default where it
     fits), else on mma.sync; both take head sizes 64 and 128.  exact (mma.sync kernel only): the
     attention weights stay 32-bit, split into three bfloat16 terms for the product with the values.
-    keep_first, head_pages, gate, sink (mma.sync kernel only): as attention_generic."""
-    _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache, gate)
+    keep_first, head_pages, gate, sink, sink_values, chunk (mma.sync kernel only): as attention_generic."""
+    _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache, gate, sink_values)
+    assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads and sink_values.is_contiguous())
+    sink = bool(sink) or sink_values is not None
     assert gate is None or gate.dtype == torch.bfloat16
     per_head = _gate_per_head(gate, out, n_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
-    plain = not (exact or keep_first or head_pages or gate is not None or sink)
+    plain = not (exact or keep_first or head_pages or gate is not None or sink or chunk)
     if tc is None:
         tc = attention_prefill_tc_supported(q, kcache, head_dim) and plain
     assert not tc or plain
@@ -960,7 +1058,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
     call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
          tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
          ptr(vcache), int(window or 0), float(scale), int(bool(exact)), int(head_pages), int(keep_first or 0), ptr(gate),
-         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), stream_ptr())
+         0 if gate is None else gate.stride(0), int(per_head), int(bool(sink)), ptr(sink_values), int(chunk or 0), stream_ptr())
     return out
 
 

@@ -16,7 +16,7 @@ import torch
 from ..cache.cache import Cache, CacheLayout
 from ..config.specs import LayerSpec, ModelSpec, PartSpec
 from ..parts.base import HostBatch, RunView, StepContext, Stream, plan_key_of
-from ..parts.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
+from ..parts.registry import BLOCKS, EMBEDDINGS, EXTRAS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
 from ..weights.loader import TensorRequest, WeightStore
 
 
@@ -33,10 +33,13 @@ class Layer:
         self.feed_forward = None if spec.feed_forward is None else \
             FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
         self.norms = {name: NORMS.get(s.kind)(s, dtype, device) for name, s in spec.norms.items()}
-        self.block = BLOCKS.get(spec.block)(self.mixer, self.feed_forward, self.norms)
+        self.extras = {name: EXTRAS.get(s.kind)(s, dtype, device) for name, s in spec.extras.items()}
+        # an arrangement that knows no extra parts is built as before
+        more = {"extras": self.extras} if self.extras else {}
+        self.block = BLOCKS.get(spec.block)(self.mixer, self.feed_forward, self.norms, **more)
 
     def parts(self):
-        return [p for p in (self.mixer, self.feed_forward) if p is not None] + list(self.norms.values())
+        return [p for p in (self.mixer, self.feed_forward) if p is not None] + list(self.norms.values()) + list(self.extras.values())
 
 
 def _requests_of(spec: ModelSpec, parts) -> List[TensorRequest]:
@@ -81,7 +84,7 @@ class Decoder:
         computing = [self.embedding, self.final_norm, self.head]
         for r in spec.schedule:
             l = self.layers[r.layer]
-            computing += [p for p in (l.block, l.mixer, l.feed_forward) if p is not None] + list(l.norms.values())
+            computing += [p for p in (l.block, l.mixer, l.feed_forward) if p is not None] + list(l.norms.values()) + list(l.extras.values())
         for part in computing:
             key = plan_key_of(part)
             if hasattr(part, "plan") and key not in seen_plans:

@@ -142,7 +142,7 @@ _SIGNATURES = {
     "gb_zero_rows": [_P, _P, _I, _I, _P],
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
     "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _I, _I, _P, _I, _L, _I, _I,
-                             _P],
+                             _P, _I, _P],
     "gb_add_dyt": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P],
     "gb_scale": [_P, _L, _F, _P],
     "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _L, _P],
@@ -163,21 +163,25 @@ _SIGNATURES = {
     "gb_gla": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _I, _F, _F, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
     "gb_gla_segment_floats": [_I, _I, _I, _I, _I],
     "gb_gla_scratch_floats": [_I, _I, _I, _I],
-    "gb_moe_router": [_P, _I, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
-    "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
-    "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
-    "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P],
+    "gb_moe_router": [_P, _I, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P],
+    "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P],
+    "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _I, _P],
+    "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _I, _L, _P],
     "gb_unary_act": [_P, _I, _L, _I, _P],
     "gb_unary_act_rows": [_P, _I, _I, _I, _L, _I, _P],
     "gb_moe_grouped_supported": [_I, _I],
     "gb_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "gb_moe_gather_rows": [_P, _L, _I, _I, _I, _P, _P, _P],
-    "gb_moe_combine_sorted": [_P, _P, _P, _I, _I, _I, _P, _I, _P],
+    "gb_moe_combine_sorted": [_P, _P, _P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _L, _P],
     "gb_moe_grouped_scratch_ints": [_I, _I, _I],
-    "gb_moe_grouped": [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P],
+    "gb_moe_grouped": [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P],
     "gb_glu_clamped": [_P, _L, _P, _I, _I, _I, _F, _P],
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
-    "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
+    "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
+    "gb_selective_scan": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "gb_selective_scan_segment_floats": [_I, _I, _I, _I],
+    "gb_norm_sandwich": [_P, _P, _I, _L, _P, _I, _L, _P, _P, _F, _P, _P, _I, _F, _P, _I, _P, _P, _I, _I, _P],
+    "gb_token_side_gate": [_P, _I, _L, _P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _P],
     "gb_pack_latent_heads": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
     "gb_latent_decode_supported": [_I, _I, _I, _I, _I],
     "gb_latent_decode_set_mma": [_I],
@@ -195,7 +199,7 @@ _SIGNATURES = {
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
     "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
     "gb_attention_decode_kept": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _I, _I, _P, _L, _I, _I,
-                                 _P],
+                                 _P, _I, _P],
     "gb_attention_decode_mma": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
     "gb_attention_decode_mma_rope": [_P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I,
                                      _P, _P, _I, _P],
@@ -206,7 +210,7 @@ _SIGNATURES = {
     "gb_gemm_tc_set_stamps": [_P, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
-    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _I, _I, _P, _L, _I, _I, _P],
+    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _I, _I, _P, _L, _I, _I, _P, _I, _P],
     "gb_attention_prefill_supported": [_I, _I, _I],
     "gb_attention_prefill_tile": [],
     "gb_attention_prefill_tc": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _L, _I, _F, _P],
@@ -217,7 +221,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_gla_segment_floats": ctypes.c_longlong, "gb_linear_walk_scratch_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_gla_segment_floats": ctypes.c_longlong, "gb_selective_scan_segment_floats": ctypes.c_longlong, "gb_linear_walk_scratch_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:

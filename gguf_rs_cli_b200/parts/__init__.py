@@ -1,10 +1,11 @@
-from . import attention, block, delta_rule, embedding, feed_forward, gla, latent_attention, norm, rotary, ssd, wkv  # noqa: F401  (register the built-in parts)
+from . import (attention, block, delta_rule, embedding, feed_forward, gla, latent_attention, norm, pair, rotary,  # noqa: F401
+               selective_scan, ssd, token_side, wkv)  # noqa: F401  (register the built-in parts)
 from .base import HostBatch, Part, RunView, StepContext, Stream, Workspace, plan_key_of
 from .linear import Linear
-from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, register_block,
-                       register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
+from .registry import (BLOCKS, EMBEDDINGS, EXTRAS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, register_block,
+                       register_embedding, register_extra, register_feed_forward, register_head, register_mixer, register_norm,
                        register_position)
 
 __all__ = ["Part", "RunView", "StepContext", "Stream", "Workspace", "Linear", "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS",
-           "HEADS", "MIXERS", "NORMS", "POSITIONS", "register_block", "register_embedding", "register_feed_forward",
+           "HEADS", "EXTRAS", "MIXERS", "NORMS", "POSITIONS", "register_block", "register_embedding", "register_extra", "register_feed_forward",
            "register_head", "register_mixer", "register_norm", "register_position"]

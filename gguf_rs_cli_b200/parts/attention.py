@@ -26,6 +26,12 @@ And for designs that smooth their projections over time and let a head attend to
 per channel on q, k and v, directly behind the projection and before the rotation, without bias or activation (`conv`
 taps; the last taps - 1 projected rows are per-sequence state); a softmax whose denominator counts one more key of
 score 0 that has no value (`sink`); and a gate of one number per head instead of one per entry (`out_gate="head"`).
+
+And for designs that cut the sequence into chunks or learn their sinks: keys in chunks of `chunk` positions counted from
+the sequence's start, a token seeing the earlier tokens of its own chunk only (in a window's place; the cache keeps a
+ring of that many positions); a sink whose score is a learned number per head, not scaled (`sink="learned"`, tensor
+`sink` [heads]); `exact=True` asks for 32-bit scores and weights where nothing else does.  These paths also take q/k/v
+biases and `shares_kv` (the layer then prepares its queries only and attends to the other run's keys and values).
 """
 from __future__ import annotations
 
@@ -48,7 +54,8 @@ class Attention(Part):
     qk_norm_eps (default None: no normalisation), q_temp (default None, or {"coef", "every"}),
     head_norm_eps (default None), keep_first (default 0), out_gate (default False), v_mix (None, "gives" or "takes"),
     v_mix_optional (the folder may hold the scalar although nothing is mixed), conv (default None; taps of a short
-    convolution on q, k and v), sink (default False), out_gate "head": one gate per head.
+    convolution on q, k and v), sink (default False; "learned": a score per head from the tensor `sink`), out_gate "head":
+    one gate per head, chunk (None or C: chunks of C positions in a window's place), exact (default False).
     tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias;
     with head_norm_eps q_norm, k_norm [hd]; with out_gate g [nh*vd, E] ("head": [nh, E]); with v_mix the scalar v_mix;
     with conv q_conv, k_conv, v_conv [channels, taps]."""
@@ -77,26 +84,33 @@ class Attention(Part):
         if not 1 <= self.conv <= 16:
             raise ValueError(f"attention: a convolution of {self.conv} taps is not supported (1..16)")
         self.sink = bool(p.get("sink", False))
+        self.sink_learned = p.get("sink") == "learned"
+        self.chunk = int(p.get("chunk") or 0)
+        if self.chunk and (self.window or p.get("keep_first")):
+            raise ValueError("attention: chunks go with neither a window nor kept first positions")
         self.v_mix = p.get("v_mix") or None
         if self.v_mix not in (None, "gives", "takes"):
             raise ValueError(f"attention: v_mix {self.v_mix!r} is not one of None, 'gives', 'takes'")
         # heads with a norm of their own, a gate, kept first positions or mixed values: prepared by one kernel
         # (norm, rotation, mixing, cache write) and attended to with 32-bit weights
         self.prepared = bool(self.head_norm_eps is not None or self.keep_first or self.out_gate or self.v_mix or self.conv > 1
-                             or self.sink)
+                             or self.sink or self.chunk or p.get("exact"))
         # where the parts of the fused projection start: q, k, v and the gate, each at a multiple of 8 rows
         self.off, rows = {}, 0
-        for n, size in (("q", self.nh * self.hd), ("k", self.nkv * self.hd), ("v", self.nkv * self.vd),
+        own = 0 if self.shares_kv else 1
+        for n, size in (("q", self.nh * self.hd), ("k", own * self.nkv * self.hd), ("v", own * self.nkv * self.vd),
                         ("g", (self.nh if self.gate_per_head else self.nh * self.vd) if self.out_gate else 0)):
             self.off[n] = (rows + 7) // 8 * 8
             rows = self.off[n] + size
         self.gate_rows = rows - self.off["g"]
-        self.conv_channels = self.off["v"] + self.nkv * self.vd      # q, k, v and the empty rows between them
+        self.conv_channels = self.off["v"] + own * self.nkv * self.vd      # q, k, v and the empty rows between them
         # normalised q and k, a query temperature or values of their own size: the exact path
         self.exact = self.prepared or self.vd != self.hd or self.qk_norm_eps is not None or self.temp_coef != 0.0
-        if self.prepared and (self.qk_norm_eps is not None or self.temp_coef != 0.0 or self.shares_kv or p.get("bias")):
-            raise ValueError("attention: head_norm_eps, keep_first, out_gate, v_mix, conv and sink go with none of qk_norm_eps, "
-                             "q_temp, shares_kv and biases")
+        if self.prepared and (self.qk_norm_eps is not None or self.temp_coef != 0.0):
+            raise ValueError("attention: head_norm_eps, keep_first, out_gate, v_mix, conv, sink, chunk and exact go with neither "
+                             "qk_norm_eps nor q_temp")
+        if self.shares_kv and self.v_mix:
+            raise ValueError("attention: a layer that reads another's keys and values has no values to mix")
         if self.exact and not self.prepared and (position is not None or self.shares_kv):
             raise ValueError("attention: qk_norm_eps, q_temp and v_head_dim go with neither a rotation nor shares_kv")
 
@@ -105,7 +119,7 @@ class Attention(Part):
 
     def reads_kv_spec(self) -> KVSpec:
         """The kind of cache this mixer can read (its own, or another run's)."""
-        return KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first)
+        return KVSpec(self.nkv, self.hd, self.window or self.chunk or None, None if self.vd == self.hd else self.vd, self.keep_first)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         return {"conv": ((self.conv - 1, self.conv_channels), "float32")} if self.conv > 1 else {}
@@ -123,7 +137,9 @@ class Attention(Part):
         if self.out_gate:
             req.append(TensorRequest(t["g"], (self.gate_rows, E)))
         if self.conv > 1:
-            req += [TensorRequest(t[n + "_conv"], (rows[n], self.conv), init="uniform:-0.6:0.6") for n in ("q", "k", "v")]
+            req += [TensorRequest(t[n + "_conv"], (rows[n], self.conv), init="uniform:-0.6:0.6") for n in names]
+        if self.sink_learned:
+            req.append(TensorRequest(t["sink"], (self.nh,), init="uniform:-1:1"))
         if self.v_mix or self.p.get("v_mix_optional"):
             req.append(TensorRequest(t["v_mix"], (), optional=not self.v_mix, init="const:0.25" if self.v_mix else None))
         return req
@@ -147,9 +163,18 @@ class Attention(Part):
         """q, k, v and the gate as one matrix, each part starting at a multiple of 8 rows (zero rows between), so that
         one product reads h once and every slice of its result is aligned."""
         t = self.spec.tensors
-        names = ["q", "k", "v"] + (["g"] if self.out_gate else [])
+        names = ["q"] + ([] if self.shares_kv else ["k", "v"]) + (["g"] if self.out_gate else [])
         mats = [store.get(req[t[n]]) for n in names]
         dt = mats[0].dtype
+        total = (self.off["g"] + self.gate_rows + 7) // 8 * 8
+        bias = None
+        if self.p.get("bias"):
+            bias = torch.zeros(total, dtype=torch.float32, device=mats[0].device)
+            for n in names:
+                if n != "g":
+                    b = store.get(req[t[n + "_bias"]])
+                    bias[self.off[n]:self.off[n] + b.numel()] = b.to(torch.float32)
+        self.sink_values = store.get(req[t["sink"]]).to(torch.float32).contiguous() if self.sink_learned else None
         parts, rows = [], 0
         for n, m in zip(names, mats):
             pad = self.off[n] - rows
@@ -160,7 +185,7 @@ class Attention(Part):
         pad = (rows + 7) // 8 * 8 - rows
         if pad:
             parts.append(torch.zeros(pad, mats[0].shape[1], dtype=dt, device=mats[0].device))
-        self.qkv = Linear(torch.cat(parts, dim=0).contiguous(), name="attn.qkvg")
+        self.qkv = Linear(torch.cat(parts, dim=0).contiguous(), bias, name="attn.qkvg")
         self.o = Linear(store.get(req[t["o"]]), name="attn.o")
         self.q_norm = self.k_norm = None
         if self.head_norm_eps is not None:
@@ -171,7 +196,7 @@ class Attention(Part):
         if self.conv > 1:
             # one convolution over all columns of q, k and v; the empty rows between them have taps of zero
             self.taps = torch.zeros(self.conv_channels, self.conv, dtype=dt, device=mats[0].device)
-            for n in ("q", "k", "v"):
+            for n in (n for n in names if n != "g"):
                 w = store.get(req[t[n + "_conv"]])
                 self.taps[self.off[n]:self.off[n] + w.shape[0]] = w.to(dt)
             self.taps_t = self.taps.t().contiguous() if dt == torch.bfloat16 else None
@@ -184,7 +209,7 @@ class Attention(Part):
 
     # ---- planning on the host
     def plan_key(self):
-        return ("attention", self.hd, self.vd, self.window, self.exact, self.prepared, self.keep_first)
+        return ("attention", self.hd, self.vd, self.window, self.exact, self.prepared, self.keep_first, self.chunk, self.sink_learned)
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
@@ -195,12 +220,16 @@ class Attention(Part):
     def _exact_tiled(self) -> bool:
         """Whether prompts of the exact path take the tiled kernel (bfloat16, keys and values of 64 or 128 entries
         both) with 32-bit attention weights; other sizes and the 32-bit mode take the general kernel."""
-        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd in (64, 128)
+        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd in (64, 128) and self._fast_masks()
+
+    def _fast_masks(self) -> bool:
+        """Whether the tiled and the decode kernel know this layer's mask and sink."""
+        return True
 
     def _exact_decode(self) -> bool:
         """Whether single tokens of the exact path take the CUDA-core decode kernel (32-bit weights; bfloat16, keys
         and values of one size that is a multiple of 16 up to 256)."""
-        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.hd <= 256
+        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.hd <= 256 and self._fast_masks()
 
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
@@ -208,9 +237,14 @@ class Attention(Part):
         if self.exact:
             # the general kernel: one block per token and head, whatever the lengths; the CUDA-core decode kernel
             # splits each sequence's pages by a rule of the longest sequence
-            max_kv = min(batch.max_kv, self.window + self.keep_first) if self.window else batch.max_kv
-            return ("cuda", kernels.decode_split_class_exact(max_kv)) if self._exact_decode() else ()
+            return ("cuda", kernels.decode_split_class_exact(self._longest_seen(batch.max_kv))) if self._exact_decode() else ()
         return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
+
+    def _longest_seen(self, max_kv: int) -> int:
+        """The most keys a token of a sequence of max_kv positions can see."""
+        if self.window:
+            return min(max_kv, self.window + self.keep_first)
+        return min(max_kv, self.chunk) if self.chunk else max_kv
 
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
         """Multiplies the weight of the norm in front of this mixer into the q/k/v matrix, where
@@ -237,8 +271,10 @@ class Attention(Part):
                                taps_t=self.taps_t)
             proj = conv
             ctx.mark("conv")
-        q, k, v = (proj[:, off["q"]:off["q"] + nh * hd], proj[:, off["k"]:off["k"] + nkv * hd],
-                   proj[:, off["v"]:off["v"] + nkv * vd])
+        q = proj[:, off["q"]:off["q"] + nh * hd]
+        k = v = None                         # a layer that reads another run's cache prepares its queries only
+        if not self.shares_kv:
+            k, v = proj[:, off["k"]:off["k"] + nkv * hd], proj[:, off["v"]:off["v"] + nkv * vd]
         v_first = first_out = None
         if self.v_mix == "gives":
             first_out = ctx.shared[self.V_FIRST] = ctx.ws.get("attn.v_first", (T, nkv * vd), proj.dtype)
@@ -254,14 +290,15 @@ class Attention(Part):
         ctx.mark("heads")
         out = ctx.ws.get("attn.out", (T, nh * vd), ctx.dtype)
         tiles = ctx.plan_of(self).get("tiles")
-        kept = dict(keep_first=self.keep_first, head_pages=run.head_pages, gate=gate, sink=self.sink)
+        kept = dict(keep_first=self.keep_first, head_pages=run.head_pages, gate=gate, sink=self.sink, sink_values=self.sink_values,
+                    chunk=self.chunk)
         if not ctx.decode and tiles is not None and self._exact_tiled() and kernels.attention_prefill_supported(q, run.k, hd):
             # prompts, keys and values of 64 or 128 entries: the tiled kernel with 32-bit weights
             kernels.attention_prefill(q, out, nh, nkv, hd, tiles, ctx.cu, ctx.starts, ctx.qlens, table, run.ring_pages,
                                       run.k, run.v, self.window or 0, self.scale, tc=False, exact=True, **kept)
         elif ctx.decode and self._exact_decode() and kernels.attention_decode_supported(q, run.k, hd):
             # single tokens: one pass over a token's keys serves the heads of a group, 32-bit weights
-            max_kv = min(ctx.max_kv, self.window + self.keep_first) if self.window else ctx.max_kv
+            max_kv = self._longest_seen(ctx.max_kv)
             splits = kernels.decode_splits_exact(T, nh, nkv, max_kv, kernels.tc_scratch(q.device).sms)
             kernels.attention_decode(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
                                      self.window or 0, self.scale, mma=False, max_kv=max_kv, splits=splits, **kept)

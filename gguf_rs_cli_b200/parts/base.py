@@ -186,6 +186,17 @@ class Stream:
 
 
 @dataclass
+class Blend:
+    """What a mixer of two branches gives a block that can finish it in the kernel that also norms it into the stream:
+    mix * (a / rms(a) * weights[0] + b / rms(b) * weights[1]), rms(v) = sqrt(mean(v^2) + eps)."""
+    a: torch.Tensor
+    b: torch.Tensor
+    weights: Tuple[torch.Tensor, torch.Tensor]
+    mix: float
+    eps: float
+
+
+@dataclass
 class DeferredNorm:
     """Rows whose RMS norm has not been applied: the consumer (a product that has folded the
     norm's weight into its matrix) scales its results per token by

@@ -136,3 +136,44 @@ class ParallelBlock:
                 raise RuntimeError("parallel: a feed-forward must give one term [tokens, width]")
             stream.more.append(term)
             ctx.mark("ff")
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """x += norm_mo(mixer(norm_m(x))); x += norm_fo(ff(norm_f(x))): every sublayer reads a norm of x and what it gives is
+    normed again on its way into x.  One kernel per sublayer does both sides of the seam: it norms the result into x
+    (32-bit) and writes the rows the next sublayer reads.  A mixer of two branches may hand over its branches unblended
+    (`forward_blend`); the same kernel then norms and blends them first.  An extra part `side`, if the layer has one, adds
+    an input of its own behind the feed-forward, normed in by `norms["side"]` (it reads x itself: the bfloat16 copy in
+    bfloat16 mode).  norms: mixer, mixer_out, and with a feed-forward feed_forward, feed_forward_out."""
+
+    norm_names = ("mixer", "mixer_out", "feed_forward", "feed_forward_out")
+    graph_class = ()
+
+    def __init__(self, mixer, feed_forward, norms, extras=None):
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        self.side = (extras or {}).get("side")
+        need = ["mixer", "mixer_out"] + (["feed_forward", "feed_forward_out"] if feed_forward is not None else []) \
+            + (["side"] if self.side is not None else [])
+        for name in need:
+            if name not in norms or not hasattr(norms[name], "add_normed"):
+                raise ValueError(f"sandwich: the layer needs a norm {name!r} that can norm a result into the stream")
+
+    def forward(self, stream: Stream, ctx: StepContext, run: RunView) -> None:
+        norms = self.norms
+        h = norms["mixer"].apply(stream, ctx)
+        ctx.mark("norm")
+        give = getattr(self.mixer, "forward_blend", None) or self.mixer.forward
+        term = give(h, ctx, run)
+        last = self.feed_forward is None
+        h = norms["mixer_out"].add_normed(stream, term, ctx, then=None if last else norms["feed_forward"], buffer="normed2",
+                                          shadow=last and self.side is not None)
+        ctx.mark("mixer_norm")
+        if not last:
+            term = self.feed_forward.forward(h, ctx)
+            norms["feed_forward_out"].add_normed(stream, term, ctx, shadow=self.side is not None)
+            ctx.mark("ff_norm")
+        if self.side is not None:
+            rows = stream.x if ctx.dtype == torch.float32 else stream.xb
+            norms["side"].add_normed(stream, self.side.forward(rows, ctx), ctx, shadow=False)
+            ctx.mark("side")

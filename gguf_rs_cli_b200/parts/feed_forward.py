@@ -111,9 +111,15 @@ class RoutedExperts(Part):
     best groups can be chosen; the `top` largest of those are, with weights score / (sum of the chosen scores + 1e-20)
     * scale.  The reference has no routed feed-forward (src/model/llama.rs:399-402 is its dense one).
 
+    Options: scores that are a softmax over all experts instead of sigmoids (`score="softmax"`); a correction per expert
+    that is added to the scores for the choice and left out of the weights (`correction=True`, tensor `correction`);
+    `identity` experts without matrices, numbered behind the others, whose result is the token's own row h (the router's
+    matrix and the correction then have experts + identity rows).
+
     params: hidden_size, experts, top, groups, keep, scale, expert_ff, limit, shared_ff, shared_limit (None: no shared
-    expert).  tensors: router [experts, E]; experts: the prefix of the experts' names (<prefix><i>.gate [F, E], .up
-    [F, E], .down [E, F]); shared: the prefix of the shared expert's (.gate, .up [Fs, E], .down [E, Fs])."""
+    expert), score ("sigmoid" or "softmax"), correction (default False), identity (default 0).  tensors: router
+    [experts + identity, E]; experts: the prefix of the experts' names (<prefix><i>.gate [F, E], .up [F, E], .down [E, F]);
+    shared: the prefix of the shared expert's (.gate, .up [Fs, E], .down [E, Fs]); correction [experts + identity]."""
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -121,7 +127,15 @@ class RoutedExperts(Part):
         self.n, self.top, self.F = int(p["experts"]), int(p["top"]), int(p["expert_ff"])
         self.groups, self.keep = int(p.get("groups") or 1), int(p.get("keep") or 1)
         self.shared_ff = p.get("shared_ff")
-        if self.n % self.groups or self.keep > self.groups or self.top > self.keep * (self.n // self.groups):
+        self.identity = int(p.get("identity") or 0)
+        self.n_all = self.n + self.identity
+        self.score = p.get("score", "sigmoid")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"moe: score {self.score!r} is not one of 'sigmoid', 'softmax'")
+        self.corrected = bool(p.get("correction", False))
+        if self.identity and self.groups != 1:
+            raise ValueError("moe: identity experts go with one group of experts")
+        if self.n_all % self.groups or self.keep > self.groups or self.top > self.keep * (self.n_all // self.groups):
             raise ValueError(f"moe: {self.top} of {self.n} experts in {self.groups} groups of which {self.keep} are kept")
 
     def _names(self):
@@ -130,13 +144,15 @@ class RoutedExperts(Part):
 
     def tensor_requests(self) -> List[TensorRequest]:
         E, F, t = self.p["hidden_size"], self.F, self.spec.tensors
-        req = [TensorRequest(t["router"], (self.n, E))]
+        req = [TensorRequest(t["router"], (self.n_all, E))]
         for name in self._names():
             req.append(TensorRequest(name, (E, F) if name.endswith(".down") else (F, E)))
         if self.shared_ff:
             Fs = int(self.shared_ff)
             req += [TensorRequest(t["shared"] + ".gate", (Fs, E)), TensorRequest(t["shared"] + ".up", (Fs, E)),
                     TensorRequest(t["shared"] + ".down", (E, Fs))]
+        if self.corrected:
+            req.append(TensorRequest(t["correction"], (self.n_all,), init="zeros"))
         return req
 
     def load(self, store: WeightStore) -> None:
@@ -149,8 +165,9 @@ class RoutedExperts(Part):
         self.w_up = torch.stack([m.to(dt) for m in mats[1::3]]).contiguous()
         self.w_down = torch.stack([m.to(dt) for m in mats[2::3]]).contiguous()
         self.shared_gate_up = self.shared_down = None
+        self.correction = store.get(req[-1]).to(torch.float32).contiguous() if self.corrected else None
         if self.shared_ff:
-            g, u, d = (store.get(r) for r in req[1 + 3 * self.n:])
+            g, u, d = (store.get(r) for r in req[1 + 3 * self.n:4 + 3 * self.n])
             self.shared_gate_up = Linear(torch.cat([g, u.to(g.dtype)], dim=0), name="moe.shared_gate_up")
             self.shared_down = Linear(d, name="moe.shared_down")
 
@@ -166,7 +183,7 @@ class RoutedExperts(Part):
         ids = ctx.ws.get("moe.ids", (T, top), torch.int32)
         weights = ctx.ws.get("moe.weights", (T, top), torch.float32)
         kernels.moe_router(h if x32 is None else x32, self.router.weight, self.groups, self.keep, top,
-                           float(self.p.get("scale", 1.0)), ids, weights)
+                           float(self.p.get("scale", 1.0)), ids, weights, softmax=self.score == "softmax", correction=self.correction)
         ctx.mark("router")
         out = ctx.ws.get("moe.out", (T, E), torch.float32)
         if self.shared_ff:
@@ -181,14 +198,15 @@ class RoutedExperts(Part):
             # the tcgen05 kernels (8,192 pairs, 16 experts of 3,584 x 4,096: 1.65 against 3.99 ms; of 2,048 x 2,048: 1.17
             # against 1.21 ms, the launches of small products fill a quarter of the device)
             kernels.moe_by_expert(h, ids, weights, self.w_gate, self.w_up, self.w_down, float(self.p["limit"]), out, ctx,
-                                  accumulate=bool(self.shared_ff))
+                                  accumulate=bool(self.shared_ff), identity=self.identity)
         elif T > self.TOKEN_BY_TOKEN and kernels.moe_grouped_supported(h, self.w_gate):
             # many tokens: pairs sorted by expert on the device, tiles of 64 pairs on the tensor cores
             kernels.moe_grouped(h, ids, weights, self.w_gate, self.w_up, self.w_down, float(self.p["limit"]), out, ctx,
-                                accumulate=bool(self.shared_ff))
+                                accumulate=bool(self.shared_ff), identity=self.identity)
         else:
             y = ctx.ws.get("moe.units", (T, top, self.F), ctx.dtype)
-            kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y)
-            kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff), ws=ctx.ws)
+            kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y, identity=self.identity)
+            kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff), ws=ctx.ws, identity=self.identity,
+                             h=h)
         ctx.mark("experts")
         return out

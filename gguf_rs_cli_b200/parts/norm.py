@@ -9,7 +9,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorRequest, WeightStore
-from .base import FUSE_MAX_TOKENS, DeferredNorm, Part, StepContext, Stream
+from .base import FUSE_MAX_TOKENS, Blend, DeferredNorm, Part, StepContext, Stream
 from .registry import register_norm
 
 
@@ -91,12 +91,32 @@ class RMSNorm(Part):
         return out
 
 
-    def add_normed(self, stream: Stream, term: torch.Tensor, ctx: StepContext) -> None:
+    def add_normed(self, stream: Stream, term, ctx: StepContext, then: Optional["RMSNorm"] = None, buffer: str = "normed",
+                   shadow: Optional[bool] = None):
         """x += term / sqrt(mean(term^2) + eps) * w: the norm of a sublayer's result on its way into the stream
         (32-bit).  In bfloat16 mode the stream's bfloat16 copy is renewed by the same kernel; sums of squares of x
-        are not kept (a deferred norm in front of the next product would need them)."""
+        are not kept (a deferred norm in front of the next product would need them).
+
+        For layers that norm a sublayer's input too: `then` is the norm in front of the next sublayer, whose rows
+        (x / rms(x) * its weight, in the step's dtype) the same kernel writes and this call returns; term may be a
+        Blend of two branches, finished in the same pass; shadow says whether the bfloat16 copy of x is wanted
+        (default: in bfloat16 mode, as before)."""
         if stream.pending is not None or stream.more:
             raise RuntimeError("rmsnorm: a term is pending on the stream")
+        if then is not None or isinstance(term, Blend) or shadow is not None:
+            if self.offset or (then is not None and (then.offset or then.p["eps"] != self.p["eps"] or then.p["size"] != self.p["size"])):
+                raise ValueError("rmsnorm: the norms of one pass must agree in size and eps and have plain weights")
+            want = ctx.dtype == torch.bfloat16 if shadow is None else bool(shadow) and ctx.dtype == torch.bfloat16
+            xb = ctx.ws.get("stream.xb", stream.x.shape, torch.bfloat16) if want else None
+            h = ctx.ws.get(buffer, stream.x.shape, ctx.dtype) if then is not None else None
+            nw = None if then is None else (then.weight if then.weight.dtype == self.weight.dtype else then.weight.to(self.weight.dtype))
+            if isinstance(term, Blend):
+                kernels.norm_sandwich(stream.x, term.a, self.weight, self.p["eps"], y2=term.b, inner_weights=term.weights,
+                                      mix=term.mix, next_weight=nw, h=h, xb=xb)
+            else:
+                kernels.norm_sandwich(stream.x, term, self.weight, self.p["eps"], next_weight=nw, h=h, xb=xb)
+            stream.xb, stream.ssq, stream.ssq_parts = xb, None, 0
+            return h
         xb = ctx.ws.get("stream.xb", stream.x.shape, torch.bfloat16) if ctx.dtype == torch.bfloat16 else None
         kernels.norm_residual_add(stream.x, term, self.weight, self.p["eps"], xb=xb)
         stream.xb, stream.ssq, stream.ssq_parts = xb, None, 0

@@ -35,6 +35,7 @@ POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+EXTRAS = Registry("extra part of a layer")      # what a block arrangement wires in beside mixer, feed-forward and norms
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
@@ -43,3 +44,4 @@ register_position = POSITIONS.register
 register_block = BLOCKS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_extra = EXTRAS.register
