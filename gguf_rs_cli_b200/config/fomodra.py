@@ -62,8 +62,8 @@ class FomodraConfig:
             if not 0 <= src < i or out[src].type != "attention" or out[src].mixer.get("kv_from") is not None:
                 raise ConfigError(f"config.json: {where} = {src} must name an earlier attention layer with keys and values of its own")
             a, b = layer.mixer, out[src].mixer
-            if any(a[k] != b[k] for k in ("kv_heads", "dim", "vdim", "rot")) or a["mask"] != b["mask"]:
-                raise ConfigError(f"config.json: {where}: layer {src} has other key/value heads, sizes, rotation or mask than layer {i}")
+            if any(a[k] != b[k] for k in ("kv_heads", "dim", "vdim", "rot")):
+                raise ConfigError(f"config.json: {where}: layer {src} has other key/value heads, sizes or rotation than layer {i}")
         bigram = None
         big = (raw.get("embedding") or {}).get("bigram") if isinstance(raw.get("embedding"), dict) else None
         if big is not None:
@@ -152,8 +152,23 @@ def _rope(m, head_dim: int) -> Optional[PartSpec]:
     return PartSpec("rope", dict(head_dim=head_dim, rotary_dim=rot["dims"], theta=rot["base"], pairing="half", scaling=scaling))
 
 
-def _attention(E: int, m, p: str, chunked: bool, bias: bool, sink: bool) -> PartSpec:
+def _cache_spans(cfg: "FomodraConfig") -> Dict[int, Optional[int]]:
+    """For every attention layer, how many of the last positions its cache must keep (None: all): the widest window among
+    the layer that owns the keys and the layers that read them."""
+    owner = {i: (l.mixer["kv_from"] if l.mixer["kv_from"] is not None else i) for i, l in enumerate(cfg.layers) if l.type == "attention"}
+    spans: Dict[int, Optional[int]] = {}
+    for i, o in owner.items():
+        size = (cfg.layers[i].mixer["mask"] or {}).get("size")
+        if o not in spans:
+            spans[o] = size
+        elif spans[o] is not None:
+            spans[o] = None if size is None else max(spans[o], size)
+    return {i: spans[o] for i, o in owner.items()}
+
+
+def _attention(E: int, m, p: str, chunked: bool, bias: bool, sink: bool, cache_span="own") -> PartSpec:
     size = (m["mask"] or {}).get("size")
+    more = {} if cache_span == "own" else {"cache_span": cache_span}
     shares = m["kv_from"] is not None
     names = ["q", "o"] + ([] if shares else ["k", "v"])
     tensors = {n: p + n for n in names}
@@ -164,11 +179,12 @@ def _attention(E: int, m, p: str, chunked: bool, bias: bool, sink: bool) -> Part
     return PartSpec("attention", dict(hidden_size=E, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"],
                                       v_head_dim=m["vdim"], scale=m["scale"], window=None if chunked else size,
                                       chunk=size if chunked else None, bias=bias, sink="learned" if sink else False,
-                                      shares_kv=shares, exact=True), tensors)
+                                      shares_kv=shares, exact=True, **more), tensors)
 
 
 def build_fomodra_spec(cfg: FomodraConfig) -> ModelSpec:
     E, layers, schedule = cfg.width, [], []
+    spans = _cache_spans(cfg)
 
     def norm(name: str) -> PartSpec:
         return PartSpec("rmsnorm", dict(size=E, eps=cfg.norm_eps), {"weight": name})
@@ -177,7 +193,7 @@ def build_fomodra_spec(cfg: FomodraConfig) -> ModelSpec:
         p, m, position = f"l{i}.mix.", layer.mixer, None
         if layer.type == "attention":
             position = _rope(m, m["dim"])
-            mixer = _attention(E, m, p, chunked=False, bias=True, sink=True)
+            mixer = _attention(E, m, p, chunked=False, bias=True, sink=True, cache_span=spans[i])
         elif layer.type == "latent_attention":
             position = _rope(m, m["rot_dim"])
             mixer = PartSpec("latent_attention", dict(hidden_size=E, heads=m["heads"], dim=m["dim"], rot_dim=m["rot_dim"],

@@ -55,7 +55,8 @@ class Attention(Part):
     head_norm_eps (default None), keep_first (default 0), out_gate (default False), v_mix (None, "gives" or "takes"),
     v_mix_optional (the folder may hold the scalar although nothing is mixed), conv (default None; taps of a short
     convolution on q, k and v), sink (default False; "learned": a score per head from the tensor `sink`), out_gate "head":
-    one gate per head, chunk (None or C: chunks of C positions in a window's place), exact (default False).
+    one gate per head, chunk (None or C: chunks of C positions in a window's place), exact (default False), cache_span
+    (when present: the positions the cache keeps, None for all, where runs with windows of their own share one cache).
     tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias;
     with head_norm_eps q_norm, k_norm [hd]; with out_gate g [nh*vd, E] ("head": [nh, E]); with v_mix the scalar v_mix;
     with conv q_conv, k_conv, v_conv [channels, taps]."""
@@ -119,7 +120,10 @@ class Attention(Part):
 
     def reads_kv_spec(self) -> KVSpec:
         """The kind of cache this mixer can read (its own, or another run's)."""
-        return KVSpec(self.nkv, self.hd, self.window or self.chunk or None, None if self.vd == self.hd else self.vd, self.keep_first)
+        # how many of the last positions the cache keeps: this layer's own reach, or `cache_span` where runs with other
+        # windows read the same keys (None: all positions)
+        span = self.p["cache_span"] if "cache_span" in self.p else (self.window or self.chunk or None)
+        return KVSpec(self.nkv, self.hd, span, None if self.vd == self.hd else self.vd, self.keep_first)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         return {"conv": ((self.conv - 1, self.conv_channels), "float32")} if self.conv > 1 else {}
