@@ -4,7 +4,7 @@ one B200.  Prints one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--no-points] [--prompt-steps 128,256] [--shape 8b|1b|13b]
-                    [--design debonex|dilalix|nazerax [--sizes 1b,8b]]
+                    [--design debonex|dilalix|nazerax|fomodra [--sizes 1b,8b]]
 
 `value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
 device with CUDA events around K decode steps (each step: index arrays host to
@@ -351,9 +351,41 @@ def nazerax_config(z):
             "layers": [pattern[i % 4] for i in range(z["layers"])]}
 
 
-DESIGN_CONFIGS = {"debonex": debonex_config, "dilalix": dilalix_config, "nazerax": nazerax_config}
+def fomodra_config(z):
+    """Attention (window of 1,024, biases, a learned sink per head), chunked attention beside a selective scan (chunks of
+    1,024; inner width twice the model's, 16 state entries per channel, a convolution of 4 taps), latent attention (window
+    of 1,024, sink, a gate per head), attention that reads the first layer's keys behind a window of its own; every layer
+    with a mixture of 16 experts and 2 identity experts (4 per token, and a shared one: Dilalix's sizes) and a per-token
+    side input of 256 columns; a pair table of 16,384 rows."""
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "shared": {"ff": z["ff"] // 4, "limit": 7.0},
+           "router": {"experts": 16, "identity": 2, "top": 4}}
+    rot = {"base": 10000.0, "dims": z["head"]}
+    attn = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+            "mask": {"size": 1024}, "rot": rot}
+    left = {**attn, "rot": {**rot, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    scan = {"inner": 2 * z["width"], "state": 16, "dt_rank": z["width"] // 16, "conv": 4}
+    latent = {"heads": z["heads"], "dim": z["latent_dim"], "rot_dim": z["rot"], "rot": {"base": 10000.0, "dims": z["rot"]},
+              "kv_rank": z["kv_rank"], "vdim": z["head"], "scale": (z["latent_dim"] + z["rot"]) ** -0.5, "mask": {"size": 1024}}
+
+    def layer(i):
+        kind = i % 4
+        if kind == 0:
+            return {"type": "attention", "mixer": attn, "mlp": moe}
+        if kind == 1:
+            return {"type": "parallel", "mixer": {"left": left, "right": scan}, "mlp": moe}
+        if kind == 2:
+            return {"type": "latent_attention", "mixer": latent, "mlp": moe}
+        return {"type": "attention", "mixer": {**attn, "mask": {"size": 512}, "kv_from": i - 3}, "mlp": moe}
+
+    return {"architecture": "Fomodra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "token_side": {"dim": 256},
+            "embedding": {"bigram": {"buckets": 16384, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [layer(i) for i in range(z["layers"])]}
+
+
+DESIGN_CONFIGS = {"debonex": debonex_config, "dilalix": dilalix_config, "nazerax": nazerax_config, "fomodra": fomodra_config}
 # the closest of the other designs (a recurrent rule and attention), which a design is measured beside
-CLOSEST = {"dilalix": ("debonex", debonex_config), "nazerax": ("dilalix-dense", dilalix_dense_config)}
+CLOSEST = {"dilalix": ("debonex", debonex_config), "nazerax": ("dilalix-dense", dilalix_dense_config),
+           "fomodra": ("dilalix", dilalix_config)}
 
 
 def stage_times(llm, lens, starts=0, reps=3):

@@ -96,6 +96,8 @@ class LatentAttention(Part):
                 self.off_g = at
             parts.append(m.to(q.dtype))
             rows = at + m.shape[0]
+        if rows % 8:                      # rows of the result that start on 16 bytes, whatever the parts' sizes
+            parts.append(torch.zeros(8 - rows % 8, q.shape[1], dtype=q.dtype, device=q.device))
         self.proj = Linear(torch.cat(parts, dim=0).contiguous(), name="latent.proj")
         self.norm_weight = norm
         self.uk = uk.reshape(H, D, C).contiguous()                           # q' = q_plain W_uk[h]: [in D, out C]

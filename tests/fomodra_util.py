@@ -94,7 +94,7 @@ def make_weights(cfg, seed=0, gain=1.3):
 
     def attention(p, m, bias, sink):
         H, D, G, Dv = m["heads"], m["dim"], m.get("kv_heads") or m["heads"], m.get("vdim") or m["dim"]
-        names = [("q", H * D, 1.5 * gain)] + ([] if m.get("kv_from") is not None else [("k", G * D, 1.5 * gain), ("v", G * Dv, gain)])
+        names = [("q", H * D, gain)] + ([] if m.get("kv_from") is not None else [("k", G * D, gain), ("v", G * Dv, gain)])
         for n, rows, gn in names:
             w[p + n] = mat(rows, E, gn)
             if bias:
@@ -118,7 +118,7 @@ def make_weights(cfg, seed=0, gain=1.3):
             attention(p, m, True, True)
         elif layer["type"] == "latent_attention":
             H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-            w[p + "q"], w[p + "dkv"], w[p + "dkv.norm"] = mat(H * (D + R), E, 1.5 * gain), mat(C + R, E, 1.5 * gain), near_one(C)
+            w[p + "q"], w[p + "dkv"], w[p + "dkv.norm"] = mat(H * (D + R), E, gain), mat(C + R, E, gain), near_one(C)
             w[p + "uk"], w[p + "uv"], w[p + "o"] = mat(H * D, C, gain), mat(H * Dv, C, gain), mat(E, H * Dv)
             w[p + "sink"], w[p + "g"] = between(H, -1.0, 2.0), mat(H, E, 2.0)
         else:
