@@ -37,6 +37,7 @@ struct LdParams {
     long long ldq;
     int H, C, R, splits, table_width, ring_pages;
     float scale;
+    int window;                   // > 0: a token sees the last `window` positions only
 };
 
 __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(const LdParams p) {
@@ -49,9 +50,10 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(const LdParam
     __nv_bfloat16* kt = reinterpret_cast<__nv_bfloat16*>(qs + size_t(H) * HDK);       // [32][KS]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = p.pos[t];
-    const int nkb = (pos >> 5) + 1;                          // blocks of 32 keys up to the token's own
+    const int lo = gb_first_visible(pos, p.window, 0);
+    const int kbf = lo >> 5, nkb = (pos >> 5) - kbf + 1;      // blocks of 32 keys from the first one seen up to the token's own
     const int per = (nkb + p.splits - 1) / p.splits;
-    const int kb0 = split * per, kb1 = min(nkb, kb0 + per);
+    const int kb0 = kbf + split * per, kb1 = min(kbf + nkb, kb0 + per);
     const int* trow = p.table + size_t(b) * p.table_width;
 
     for (int i = threadIdx.x; i < H * HDK; i += LD_THREADS)
@@ -71,11 +73,11 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(const LdParam
         for (int i = threadIdx.x; i < 32 * pieces; i += LD_THREADS) {
             const int r = i / pieces, c8 = i - r * pieces, j = kb * 32 + r;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j <= pos) v = *reinterpret_cast<const uint4*>(p.cache + gb_kv_offset(trow, p.ring_pages, j, 0, 1, HDK) + 8 * c8);
+            if (j <= pos && j >= lo) v = *reinterpret_cast<const uint4*>(p.cache + gb_kv_offset(trow, p.ring_pages, j, 0, 1, HDK) + 8 * c8);
             *reinterpret_cast<uint4*>(kt + r * KS + 8 * c8) = v;
         }
         __syncthreads();
-        const bool valid = kb * 32 + lane <= pos;
+        const bool valid = kb * 32 + lane <= pos && kb * 32 + lane >= lo;
 #pragma unroll
         for (int hi = 0; hi < LD_HW; ++hi) {
             const int h = warp + LD_WARPS * hi;
@@ -181,9 +183,10 @@ __global__ void __launch_bounds__(LM_THREADS) latent_decode_mma_kernel(const LdP
     __nv_bfloat16* kt = qt + 16 * KS;                                          // [32][KS]: 32 cached rows
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = p.pos[t];
-    const int nkb = (pos >> 5) + 1;
+    const int lo = gb_first_visible(pos, p.window, 0);
+    const int kbf = lo >> 5, nkb = (pos >> 5) - kbf + 1;      // blocks of 32 keys from the first one seen up to the token's own
     const int per = (nkb + p.splits - 1) / p.splits;
-    const int kb0 = split * per, kb1 = min(nkb, kb0 + per);
+    const int kb0 = kbf + split * per, kb1 = min(kbf + nkb, kb0 + per);
     const int* trow = p.table + size_t(b) * p.table_width;
     const int pieces = HDK / 8;
     for (int i = threadIdx.x; i < 16 * pieces; i += LM_THREADS) {
@@ -204,7 +207,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_decode_mma_kernel(const LdP
         for (int i = threadIdx.x; i < 32 * pieces; i += LM_THREADS) {
             const int r = i / pieces, c8 = i - r * pieces, j = kb * 32 + r;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j <= pos) v = *reinterpret_cast<const uint4*>(p.cache + gb_kv_offset(trow, p.ring_pages, j, 0, 1, HDK) + 8 * c8);
+            if (j <= pos && j >= lo) v = *reinterpret_cast<const uint4*>(p.cache + gb_kv_offset(trow, p.ring_pages, j, 0, 1, HDK) + 8 * c8);
             *reinterpret_cast<uint4*>(kt + r * KS + 8 * c8) = v;
         }
         __syncthreads();
@@ -229,8 +232,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_decode_mma_kernel(const LdP
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int ka = key0 + 8 * j;
-            if (ka > pos) s[j][0] = s[j][2] = -INFINITY;
-            if (ka + 1 > pos) s[j][1] = s[j][3] = -INFINITY;
+            if (ka > pos || ka < lo) s[j][0] = s[j][2] = -INFINITY;
+            if (ka + 1 > pos || ka + 1 < lo) s[j][1] = s[j][3] = -INFINITY;
             mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
             mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
         }
@@ -304,9 +307,12 @@ __global__ void __launch_bounds__(LM_THREADS) latent_decode_mma_kernel(const LdP
     }
 }
 
-// out[t, h, :] = sum_s mix_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in order; padding tokens give zeros.
+// out[t, h, :] = sum_s mix_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in order; padding tokens give zeros.  sink
+// [H] (or null): the denominator also counts e^(sink_h - M), a key without a value.  gate [T, H] rows ldg apart (or
+// null): the head's result is multiplied by sigmoid(gate).
 __global__ void latent_decode_merge_kernel(const float* __restrict__ scratch, const int* __restrict__ seq_of,
-                                           __nv_bfloat16* __restrict__ out, long long ldo, int H, int C, int splits) {
+                                           __nv_bfloat16* __restrict__ out, long long ldo, int H, int C, int splits,
+                                           const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, long long ldg) {
     const int t = blockIdx.x, h = blockIdx.y;
     __nv_bfloat16* o = out + size_t(t) * ldo + size_t(h) * C;
     if (seq_of[t] < 0) {
@@ -321,13 +327,24 @@ __global__ void latent_decode_merge_kernel(const float* __restrict__ scratch, co
         const float ms = base[size_t(s) * (C + 2) + C];
         if (ms != -INFINITY) L += base[size_t(s) * (C + 2) + C + 1] * expf(ms - M);
     }
+    float f = 1.f;                       // what the sums are multiplied by: a sink above every score brings them down to its level
+    if (sink && M != -INFINITY) {
+        const float sv = sink[h];
+        if (sv > M) {
+            f = expf(M - sv);
+            L = L * f + 1.f;
+        } else {
+            L += expf(sv - M);
+        }
+    }
+    if (gate) f *= 1.f / (1.f + expf(-__bfloat162float(gate[size_t(t) * ldg + h])));
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         float v = 0.f;
         for (int s = 0; s < splits; ++s) {
             const float ms = base[size_t(s) * (C + 2) + C];
             if (ms != -INFINITY) v += base[size_t(s) * (C + 2) + c] * expf(ms - M);
         }
-        o[c] = __float2bfloat16_rn(v / L);
+        o[c] = __float2bfloat16_rn(v * f / L);
     }
 }
 
@@ -356,9 +373,12 @@ GB_API long long gb_latent_decode_scratch_floats(int T, int H, int C, int splits
 
 // q: [T, H*(C+R)] bf16 (each head: q' of C entries, then the rotated part); out: [T, H*C] bf16; cache: the latent
 // rows, [pages, 1, 64, C+R] bf16.  splits: parts of each token's keys (blocks of 32 keys are shared out evenly).
+// window > 0: the last `window` positions only; sink float [H] and gate bf16 [T, H] (rows ldg apart), each or null: see the merge.
 GB_API int gb_latent_decode(const void* q, long long ldq, void* out, long long ldo, int T, int H, int C, int R,
                             const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
-                            const void* cache, float scale, int splits, float* scratch, cudaStream_t stream) {
+                            const void* cache, float scale, int splits, float* scratch, int window, const float* sink,
+                            const void* gate, long long ldg, cudaStream_t stream) {
+    GB_REQUIRE(window >= 0, "gb_latent_decode: a negative window");
     GB_REQUIRE(gb_latent_decode_supported(H, C, R, GB_BF16, GB_BF16), "gb_latent_decode: sizes heads=%d kv_rank=%d rot_dim=%d are not supported", H, C, R);
     GB_REQUIRE(splits >= 1 && splits <= 65535 && scratch && table_width > 0 && ring_pages > 0, "gb_latent_decode: bad arguments");
     GB_REQUIRE((ldq % 2) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(scratch) & 7) == 0,
@@ -367,7 +387,7 @@ GB_API int gb_latent_decode(const void* q, long long ldq, void* out, long long l
     LdParams p;
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.seq_of = seq_of; p.pos = pos; p.table = table;
     p.scratch = scratch; p.ldq = ldq; p.H = H; p.C = C; p.R = R; p.splits = splits; p.table_width = table_width;
-    p.ring_pages = ring_pages; p.scale = scale;
+    p.ring_pages = ring_pages; p.scale = scale; p.window = window;
     if (g_latent_decode_mma && latent_decode_mma_fits(H, C, R)) {
         const size_t smem_mma = size_t(48) * ld_row_stride(C + R) * 2;
         static bool configured_mma = false;
@@ -378,7 +398,7 @@ GB_API int gb_latent_decode(const void* q, long long ldq, void* out, long long l
         }
         latent_decode_mma_kernel<<<dim3(T, splits), LM_THREADS, smem_mma, stream>>>(p);
         GB_LAUNCH_OK("gb_latent_decode (tensor cores)");
-        latent_decode_merge_kernel<<<dim3(T, H), 128, 0, stream>>>(scratch, seq_of, (__nv_bfloat16*)out, ldo, H, C, splits);
+        latent_decode_merge_kernel<<<dim3(T, H), 128, 0, stream>>>(scratch, seq_of, (__nv_bfloat16*)out, ldo, H, C, splits, sink, (const __nv_bfloat16*)gate, ldg);
         GB_LAUNCH_OK("gb_latent_decode (merge)");
         return 0;
     }
@@ -391,7 +411,7 @@ GB_API int gb_latent_decode(const void* q, long long ldq, void* out, long long l
     }
     latent_decode_kernel<<<dim3(T, splits), LD_THREADS, smem, stream>>>(p);
     GB_LAUNCH_OK("gb_latent_decode");
-    latent_decode_merge_kernel<<<dim3(T, H), 128, 0, stream>>>(scratch, seq_of, (__nv_bfloat16*)out, ldo, H, C, splits);
+    latent_decode_merge_kernel<<<dim3(T, H), 128, 0, stream>>>(scratch, seq_of, (__nv_bfloat16*)out, ldo, H, C, splits, sink, (const __nv_bfloat16*)gate, ldg);
     GB_LAUNCH_OK("gb_latent_decode (merge)");
     return 0;
 }

@@ -28,7 +28,7 @@ constexpr int SS_SEGMENT = 128;  // tokens per segment of a long prompt
 struct ScanParams {
     const void *x, *z;            // [T, inner] each: the inputs behind convolution and activation, and the gate's rows
     long long ldx, ldz;
-    const float* low;             // [T, R + 2N] float32: B from column R on, C from column R + N on
+    const void* low;              // [T, R + 2N] of low_dtype: B from column R on, C from column R + N on
     long long ldl;
     const float* dt;              // [T, inner] float32, before bias and softplus
     long long lddt;
@@ -38,7 +38,7 @@ struct ScanParams {
     long long ldo;
     const int *cu, *slots, *qlens;
     float* seg;                   // segments of long prompts: per (sequence, segment) S_end [inner, N], then sum of dt [inner]
-    int dtype, out_dtype, inner, N, R, lpc;
+    int dtype, low_dtype, out_dtype, inner, N, R, lpc;
     int mode;                     // 0: whole sequences; 1: segments from zero, keep end state and sum of dt; 2: segments from their true state
     int max_segments;
 };
@@ -88,9 +88,9 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanPa
         __syncthreads();
         for (int i = threadIdx.x; i < n * N; i += SS_THREADS) {
             const int j = i / N, e = i - j * N;
-            const float* row = p.low + size_t(first + t0 + j) * p.ldl + p.R;
-            bs[j * N + e] = row[e];
-            cs[j * N + e] = row[N + e];
+            const size_t row = size_t(first + t0 + j) * p.ldl + p.R;
+            bs[j * N + e] = gb_load(p.low, p.low_dtype, row + e);
+            cs[j * N + e] = gb_load(p.low, p.low_dtype, row + N + e);
         }
         for (int i = threadIdx.x; i < n * cpb; i += SS_THREADS) {
             const int j = i / cpb, cc = c0 + (i - j * cpb);
@@ -169,15 +169,15 @@ GB_API long long gb_selective_scan_segment_floats(int B, int max_qlen, int inner
     return (long long)B * n_seg * inner * (N + 1);
 }
 
-// x, z [T, inner] (dtype, rows ldx / ldz apart); low float32 [T, R + 2N]; dt float32 [T, inner]; dt_bias [inner], a_log
+// x, z [T, inner] (dtype, rows ldx / ldz apart); low [T, R + 2N] of low_dtype; dt float32 [T, inner]; dt_bias [inner], a_log
 // [inner, N], skip [inner] float32; state float32 [slots, inner, N], read and renewed; out [T, inner] of out_dtype.
 // seg_scratch: gb_selective_scan_segment_floats(B, max_qlen, inner, N) floats, or null (sequences walked whole).
-GB_API int gb_selective_scan(const void* x, long long ldx, const void* z, long long ldz, int dtype, const float* low, long long ldl,
-                             int R, int N, const float* dt, long long lddt, const float* dt_bias, const float* a_log,
+GB_API int gb_selective_scan(const void* x, long long ldx, const void* z, long long ldz, int dtype, const void* low, int low_dtype,
+                             long long ldl, int R, int N, const float* dt, long long lddt, const float* dt_bias, const float* a_log,
                              const float* skip, float* state, void* out, long long ldo, int out_dtype, const int* cu,
                              const int* slots, const int* qlens, int T, int B, int inner, int max_qlen, float* seg_scratch,
                              cudaStream_t stream) {
-    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(out_dtype), "gb_selective_scan: bad dtype");
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(out_dtype) && gb_is_dtype(low_dtype), "gb_selective_scan: bad dtype");
     GB_REQUIRE(inner > 0 && N > 0 && N <= SS_MAX_STATE && R >= 0, "gb_selective_scan: bad sizes inner=%d state=%d (1..%d)", inner, N, SS_MAX_STATE);
     GB_REQUIRE(x && z && low && dt && dt_bias && a_log && skip && state && out && cu && slots && qlens, "gb_selective_scan: arguments missing");
     if (B == 0 || T == 0) return 0;
@@ -187,7 +187,7 @@ GB_API int gb_selective_scan(const void* x, long long ldx, const void* z, long l
     ScanParams p;
     p.x = x; p.z = z; p.ldx = ldx; p.ldz = ldz; p.low = low; p.ldl = ldl; p.dt = dt; p.lddt = lddt; p.dt_bias = dt_bias;
     p.a_log = a_log; p.skip = skip; p.state = state; p.out = out; p.ldo = ldo; p.cu = cu; p.slots = slots; p.qlens = qlens;
-    p.seg = seg_scratch; p.dtype = dtype; p.out_dtype = out_dtype; p.inner = inner; p.N = N; p.R = R; p.lpc = lpc;
+    p.seg = seg_scratch; p.dtype = dtype; p.low_dtype = low_dtype; p.out_dtype = out_dtype; p.inner = inner; p.N = N; p.R = R; p.lpc = lpc;
     p.max_segments = (max_qlen + SS_SEGMENT - 1) / SS_SEGMENT;
     const size_t smem = size_t(SS_CH) * (2 * N + 3 * cpb) * sizeof(float);
     const unsigned blocks = unsigned((inner + cpb - 1) / cpb);

@@ -644,20 +644,27 @@ def latent_decode_class(max_kv: int) -> int:
 
 
 def latent_decode(qa: torch.Tensor, out: torch.Tensor, n_heads: int, kv_rank: int, rot_dim: int, ctx, table: torch.Tensor,
-                  ring_pages: int, cache: torch.Tensor, scale: float) -> torch.Tensor:
+                  ring_pages: int, cache: torch.Tensor, scale: float, window: int = 0, sink_values: Optional[torch.Tensor] = None,
+                  gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Latent attention of single tokens: qa [T, heads*(kv_rank + rot_dim)] (queries in the latent's space, then the
     rotated part), cache rows [kv_rank + rot_dim]; out [T, heads*kv_rank] is the mix of the rows' first kv_rank
     entries.  One pass over each token's rows serves all heads; the rows are split over CTAs (two blocks of 32 keys or
-    more per split, while two CTAs per SM hold the step) and merged in order."""
-    _cuda(qa, out, table, cache)
+    more per split, while two CTAs per SM hold the step) and merged in order.  window: the last `window` positions only;
+    sink_values float32 [heads]: one more key without a value of that score in the denominator; gate bfloat16 [T, heads]:
+    a head's result times its sigmoid."""
+    _cuda(qa, out, table, cache, sink_values, gate)
+    assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads and sink_values.is_contiguous())
+    assert gate is None or (gate.dtype == torch.bfloat16 and gate.shape == (qa.shape[0], n_heads) and gate.stride(1) == 1)
     T = qa.shape[0]
     assert qa.dtype == out.dtype == cache.dtype == torch.bfloat16 and qa.stride(1) == 1 and out.stride(1) == 1
     assert qa.shape[1] == n_heads * (kv_rank + rot_dim) and out.shape == (T, n_heads * kv_rank) and cache.shape[-1] == kv_rank + rot_dim
     lib = native.library()
-    splits = max(1, min(latent_decode_class(ctx.max_kv), 64, (2 * tc_scratch(qa.device).sms) // max(T, 1)))
+    seen = min(ctx.max_kv, window + 31) if window else ctx.max_kv
+    splits = max(1, min(latent_decode_class(seen), 64, (2 * tc_scratch(qa.device).sms) // max(T, 1)))
     scratch = ctx.ws.get("latent.partial", (lib.gb_latent_decode_scratch_floats(T, n_heads, kv_rank, splits),), torch.float32)
     call("gb_latent_decode", ptr(qa), qa.stride(0), ptr(out), out.stride(0), T, n_heads, kv_rank, rot_dim, ptr(ctx.seq_of),
-         ptr(ctx.pos), ptr(table), table.shape[1], ring_pages, ptr(cache), float(scale), splits, ptr(scratch), stream_ptr())
+         ptr(ctx.pos), ptr(table), table.shape[1], ring_pages, ptr(cache), float(scale), splits, ptr(scratch), int(window or 0),
+         ptr(sink_values), ptr(gate), 0 if gate is None else gate.stride(0), stream_ptr())
     return out
 
 
@@ -678,13 +685,13 @@ def selective_scan(x: torch.Tensor, z: torch.Tensor, low: torch.Tensor, dt_rank:
                    ctx) -> torch.Tensor:
     """The selective scan per channel c and state entry n, from and into state [slots, inner, n_state] (float32):
     dt' = softplus(dt + dt_bias); S[c, n] <- exp(-exp(a_log[c, n]) dt'_c) S[c, n] + dt'_c x_c B_n; y_c = sum_n S[c, n] C_n +
-    skip_c x_c; out = y * silu(z).  x, z [T, inner]; low float32 [T, dt_rank + 2 n_state] holds B and C behind its first
+    skip_c x_c; out = y * silu(z).  x, z [T, inner]; low [T, dt_rank + 2 n_state] holds B and C behind its first
     dt_rank columns; dt float32 [T, inner]; dt_bias, skip [inner], a_log [inner, n_state] float32.  Prompts of more
     than 256 tokens run in segments of 128 side by side (three launches)."""
     _cuda(x, z, low, dt, dt_bias, a_log, skip, state, out)
     T, inner = x.shape
     assert z.shape == (T, inner) and x.dtype == z.dtype and x.stride(1) == 1 and z.stride(1) == 1
-    assert low.dtype == torch.float32 and low.shape == (T, dt_rank + 2 * n_state) and low.stride(1) == 1
+    assert low.shape == (T, dt_rank + 2 * n_state) and low.stride(1) == 1
     assert dt.dtype == torch.float32 and dt.shape == (T, inner) and dt.stride(1) == 1
     for t, shape in ((dt_bias, (inner,)), (a_log, (inner, n_state)), (skip, (inner,))):
         assert t.dtype == torch.float32 and t.shape == shape and t.is_contiguous()
@@ -692,7 +699,7 @@ def selective_scan(x: torch.Tensor, z: torch.Tensor, low: torch.Tensor, dt_rank:
     assert out.shape == (T, inner) and out.stride(1) == 1
     n = native.library().gb_selective_scan_segment_floats(ctx.B, int(ctx.max_qlen), inner, n_state)
     seg = ctx.ws.get("scan.segments", (n,), torch.float32) if n else None
-    call("gb_selective_scan", ptr(x), x.stride(0), ptr(z), z.stride(0), dtype_code(x), ptr(low), low.stride(0), int(dt_rank),
+    call("gb_selective_scan", ptr(x), x.stride(0), ptr(z), z.stride(0), dtype_code(x), ptr(low), dtype_code(low), low.stride(0), int(dt_rank),
          int(n_state), ptr(dt), dt.stride(0), ptr(dt_bias), ptr(a_log), ptr(skip), ptr(state), ptr(out), out.stride(0),
          dtype_code(out), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), T, ctx.B, inner, int(ctx.max_qlen), ptr(seg), stream_ptr())
     if seg is not None:

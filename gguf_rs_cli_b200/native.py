@@ -178,7 +178,7 @@ _SIGNATURES = {
     "gb_glu_clamped": [_P, _L, _P, _I, _I, _I, _F, _P],
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
-    "gb_selective_scan": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "gb_selective_scan": [_P, _L, _P, _L, _I, _P, _I, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "gb_selective_scan_segment_floats": [_I, _I, _I, _I],
     "gb_norm_sandwich": [_P, _P, _I, _L, _P, _I, _L, _P, _P, _F, _P, _P, _I, _F, _P, _I, _P, _P, _I, _I, _P],
     "gb_token_side_gate": [_P, _I, _L, _P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _P],
@@ -186,7 +186,7 @@ _SIGNATURES = {
     "gb_latent_decode_supported": [_I, _I, _I, _I, _I],
     "gb_latent_decode_set_mma": [_I],
     "gb_latent_decode_scratch_floats": [_I, _I, _I, _I],
-    "gb_latent_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P],
+    "gb_latent_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _I, _P, _P, _L, _P],
     "gb_head_matmul": [_P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _I, _I, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],

@@ -130,12 +130,13 @@ class LatentAttention(Part):
 
     def _fast_decode(self) -> bool:
         """Whether single tokens take the kernel that serves all heads from one pass over the latent rows."""
-        return not (self.window or self.sink or self.gated) and kernels.latent_decode_supported(self.H, self.C, self.R, self.dtype)
+        return kernels.latent_decode_supported(self.H, self.C, self.R, self.dtype)
 
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each token's keys by a rule of the longest sequence; the general kernel launches one
         block per token and head whatever the lengths."""
-        return ("latent", kernels.latent_decode_class(batch.max_kv)) if self._fast_decode() else ()
+        seen = min(batch.max_kv, self.window + 31) if self.window else batch.max_kv
+        return ("latent", kernels.latent_decode_class(seen)) if self._fast_decode() else ()
 
     def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
         H, D, R, Dv, C = self.H, self.D, self.R, self.Dv, self.C
@@ -173,7 +174,8 @@ class LatentAttention(Part):
         kernels.head_matmul(q, D + R, self.uk, qa, C + R)
         mix = ctx.ws.get("latent.mix", (T, H * C), ctx.dtype)
         if ctx.decode and self._fast_decode():
-            kernels.latent_decode(qa, mix, H, C, R, ctx, table, run.ring_pages, run.k, float(self.p["scale"]))
+            kernels.latent_decode(qa, mix, H, C, R, ctx, table, run.ring_pages, run.k, float(self.p["scale"]), window=self.window or 0,
+                                  **more)
         else:
             kernels.attention_generic(qa, mix, H, 1, C + R, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, None,
                                       self.window or 0, float(self.p["scale"]), v_dim=C, **more)

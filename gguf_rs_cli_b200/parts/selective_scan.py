@@ -6,8 +6,9 @@ W_in h is [x | z], inner entries each.  x passes a short causal convolution per 
 A = -exp(A_log) [inner, state], per channel c and state entry n
     S[c, n] <- exp(dt'_c A[c, n]) S[c, n] + dt'_c x_c B_n;    y_c = sum_n S[c, n] C_n + D_c x_c,
 and the mixer gives W_o (y * SiLU(z)).  S (32-bit) and the convolution's last taps - 1 inputs are per-sequence state.
-The low-rank product and the step sizes' product keep 32-bit results; step sizes, decays and every sum of the recurrence
-are 32-bit (csrc/selective_scan.cu).  The reference has no such mixer (src/model/llama.rs has attention only).
+The projections run in the step's number format; the step sizes' product keeps 32-bit results, and step sizes with
+their softplus, decays with their exponentials, the state and every sum of the recurrence are 32-bit
+(csrc/selective_scan.cu).  The reference has no such mixer (src/model/llama.rs has attention only).
 """
 from __future__ import annotations
 
@@ -65,8 +66,7 @@ class SelectiveScan(Part):
         self.taps_t = self.taps.t().contiguous() if dt == torch.bfloat16 else None      # tap by tap, for 16-byte loads
         self.conv_bias = w["conv_bias"].to(dt).contiguous()
         self.low = Linear(w["x"], name="scan.low")
-        # the step sizes' product reads the low-rank result's first columns, which are 32-bit: its matrix is kept so too
-        self.dt_proj = Linear(w["dt"].to(torch.float32).contiguous(), name="scan.dt")
+        self.dt_proj = Linear(w["dt"].to(dt).contiguous(), name="scan.dt")
         self.dt_bias = w["dt_bias"].to(torch.float32).contiguous()
         self.a_log = w["A_log"].to(torch.float32).contiguous()
         self.skip = w["D"].to(torch.float32).contiguous()
@@ -83,7 +83,7 @@ class SelectiveScan(Part):
         carried = ctx.state(f"run{run.index}.conv") if self.K > 1 else None
         kernels.short_conv(proj[:, :I], self.taps, carried, ctx, x, taps_t=self.taps_t, bias=self.conv_bias, activation="silu")
         ctx.mark("conv")
-        low = self.low(x, ctx, out_dtype=torch.float32)
+        low = self.low(x, ctx)
         dt = self.dt_proj(low[:, :R], ctx, out_dtype=torch.float32)
         ctx.mark("low_rank")
         gated = ctx.ws.get("scan.gated", (T, I), ctx.dtype)
