@@ -177,11 +177,15 @@ class Decoder:
         else:
             stream = make(ctx.tokens, ctx) if make else Stream(self.embedding.forward(ctx.tokens, ctx))
         ctx.mark("embed")
-        for view in runs:
+        for i, view in enumerate(runs):
             ctx.mark_detail = view.index == 0         # stages are stamped in the first run only, as the reference does
             if view.add_input:
                 stream.more.append(x0)
                 stream.drop_shadow()
+                stream.normed = None
+            # a block whose last kernel can also norm the rows for the block behind it is told that block's first norm
+            after = runs[i + 1] if i + 1 < len(runs) else None
+            stream.next_norm = None if after is None or after.add_input else self.layers[after.layer].norms.get("mixer")
             self.layers[view.layer].block.forward(stream, ctx, view)
         ctx.mark_detail = True
         ctx.mark("layers")

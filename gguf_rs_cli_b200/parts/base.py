@@ -180,6 +180,10 @@ class Stream:
         self.xb: Optional[torch.Tensor] = None
         self.ssq: Optional[torch.Tensor] = None
         self.ssq_parts = 0
+        # The norm that the next run's block applies first (set by the decoder before every run; None behind the last),
+        # and, when a block's last kernel has already applied it, (that norm, its rows): valid while x is unchanged.
+        self.next_norm = None
+        self.normed: Optional[Tuple[object, torch.Tensor]] = None
 
     def drop_shadow(self) -> None:
         self.xb, self.ssq, self.ssq_parts = None, None, 0

@@ -159,21 +159,40 @@ class SandwichBlock:
             if name not in norms or not hasattr(norms[name], "add_normed"):
                 raise ValueError(f"sandwich: the layer needs a norm {name!r} that can norm a result into the stream")
 
+    def _last(self, norm, stream: Stream, term, ctx: StepContext, **kw) -> None:
+        """The layer's last sum; its kernel also norms the rows for the next run's block where that block begins with a
+        norm of the same kind."""
+        then = stream.next_norm
+        fits = then is not None and type(then) is type(norm) and not getattr(then, "offset", 0.0) \
+            and (then.p["size"], then.p["eps"]) == (norm.p["size"], norm.p["eps"])
+        h = norm.add_normed(stream, term, ctx, then=then if fits else None, buffer="normed", **kw)
+        stream.normed = (then, h) if fits else None
+
     def forward(self, stream: Stream, ctx: StepContext, run: RunView) -> None:
         norms = self.norms
-        h = norms["mixer"].apply(stream, ctx)
+        if stream.normed is not None and stream.normed[0] is norms["mixer"] and stream.pending is None and not stream.more:
+            h = stream.normed[1]                      # the block in front has normed these rows already
+        else:
+            h = norms["mixer"].apply(stream, ctx)
+        stream.normed = None
         ctx.mark("norm")
         give = getattr(self.mixer, "forward_blend", None) or self.mixer.forward
         term = give(h, ctx, run)
-        last = self.feed_forward is None
-        h = norms["mixer_out"].add_normed(stream, term, ctx, then=None if last else norms["feed_forward"], buffer="normed2",
-                                          shadow=last and self.side is not None)
+        bare, side = self.feed_forward is None, self.side is not None
+        if bare and not side:
+            self._last(norms["mixer_out"], stream, term, ctx, shadow=False)
+        else:
+            h = norms["mixer_out"].add_normed(stream, term, ctx, then=None if bare else norms["feed_forward"], buffer="normed2",
+                                              shadow=bare and side)
         ctx.mark("mixer_norm")
-        if not last:
+        if not bare:
             term = self.feed_forward.forward(h, ctx)
-            norms["feed_forward_out"].add_normed(stream, term, ctx, shadow=self.side is not None)
+            if side:
+                norms["feed_forward_out"].add_normed(stream, term, ctx, shadow=True)
+            else:
+                self._last(norms["feed_forward_out"], stream, term, ctx, shadow=False)
             ctx.mark("ff_norm")
-        if self.side is not None:
+        if side:
             rows = stream.x if ctx.dtype == torch.float32 else stream.xb
-            norms["side"].add_normed(stream, self.side.forward(rows, ctx), ctx, shadow=False)
+            self._last(norms["side"], stream, self.side.forward(rows, ctx), ctx, shadow=False)
             ctx.mark("side")
