@@ -46,14 +46,14 @@ WIDE = {
     "embedding": {"bigram": {"buckets": 1000, "mul_prev": 9999991, "mul_cur": 3}},
     "layers": [
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.2, "mask": {"size": 70},
-                                        "rot": {"base": 10000.0, "dims": 64}}, "mlp": _moe(8, 2, 2, 64, 1.0, (96, 2.0))},
+                                        "rot": {"base": 10000.0, "dims": 64}}, "mlp": _moe(8, 2, 3, 48, 1.25, (80, 2.5))},
         {"type": "parallel", "mixer": {"left": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.15, "mask": {"size": 96},
                                                 "rot": {"base": 5000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 128}}},
-                                       "right": {"inner": 512, "state": 16, "dt_rank": 16, "conv": 4}}, "mlp": _moe(8, 0, 2, 64, 1.0)},
+                                       "right": {"inner": 512, "state": 16, "dt_rank": 16, "conv": 4}}, "mlp": _moe(8, 0, 2, 56, 1.5)},
         {"type": "latent_attention", "mixer": {"heads": 4, "dim": 48, "rot_dim": 16, "vdim": 64, "kv_rank": 64, "scale": 0.2,
                                                "mask": {"size": 100}, "rot": {"base": 5000.0, "dims": 16}}, "mlp": _moe(4, 4, 2, 32, 1.5, (64, 1.0))},
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.15, "mask": {"size": 150}, "kv_from": 0,
-                                        "rot": {"base": 10000.0, "dims": 64}}, "mlp": _moe(8, 2, 2, 64, 1.0)},
+                                        "rot": {"base": 10000.0, "dims": 64}}, "mlp": _moe(6, 1, 2, 72, 0.75)},
         {"type": "parallel", "mixer": {"left": {"heads": 4, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.2, "mask": {"size": 64},
                                                 "rot": {"base": 100.0, "dims": 32}},
                                        "right": {"inner": 256, "state": 64, "dt_rank": 8, "conv": 2}}, "mlp": None},
