@@ -46,8 +46,11 @@ struct ScanParams {
 
 __device__ __forceinline__ float ss_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
+// FULL: the state has a whole number of lanes' shares (N % SS_NS == 0): no entry is left out, and a lane reads its B and C
+// entries of a token as four 16-byte pieces each.
+template <bool FULL>
 __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanParams p) {
-    extern __shared__ float ss_sm[];
+    extern __shared__ __align__(16) float ss_sm[];
     const int b = blockIdx.y;
     const int slot = p.slots[b];
     if (slot < 0) return;
@@ -87,19 +90,20 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanPa
     for (int t0 = 0; t0 < n_tok; t0 += SS_CH) {
         const int n = min(SS_CH, n_tok - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < n * N; i += SS_THREADS) {
-            const int j = i / N, e = i - j * N;
-            const size_t row = size_t(first + t0 + j) * p.ldl + p.R;
-            bs[j * N + e] = gb_load(p.low, p.low_dtype, row + e);
-            cs[j * N + e] = gb_load(p.low, p.low_dtype, row + N + e);
-        }
-        for (int i = threadIdx.x; i < n * cpb; i += SS_THREADS) {
-            const int j = i / cpb, cc = c0 + (i - j * cpb);
+        for (int j = 0; j < n; ++j) {
             const size_t t = size_t(first + t0 + j);
-            const bool in = cc < p.inner;
-            dts[i] = in ? ss_softplus(p.dt[t * p.lddt + cc] + p.dt_bias[cc]) : 0.f;
-            xs[i] = in ? gb_load(p.x, p.dtype, t * p.ldx + cc) : 0.f;
-            zs[i] = in && p.mode != 1 ? gb_load(p.z, p.dtype, t * p.ldz + cc) : 0.f;
+            const size_t row = t * p.ldl + p.R;
+            for (int e = threadIdx.x; e < N; e += SS_THREADS) {
+                bs[j * N + e] = gb_load(p.low, p.low_dtype, row + e);
+                cs[j * N + e] = gb_load(p.low, p.low_dtype, row + N + e);
+            }
+            for (int i = threadIdx.x; i < cpb; i += SS_THREADS) {
+                const int cc = c0 + i;
+                const bool in = cc < p.inner;
+                dts[j * cpb + i] = in ? ss_softplus(p.dt[t * p.lddt + cc] + p.dt_bias[cc]) : 0.f;
+                xs[j * cpb + i] = in ? gb_load(p.x, p.dtype, t * p.ldx + cc) : 0.f;
+                zs[j * cpb + i] = in && p.mode != 1 ? gb_load(p.z, p.dtype, t * p.ldz + cc) : 0.f;
+            }
         }
         __syncthreads();
         for (int j = 0; j < n; ++j) {
@@ -108,11 +112,27 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanPa
             const float* bj = bs + j * N + n0;
             const float* cj = cs + j * N + n0;
             float y = 0.f;
+            if (FULL) {
+                float ys[4] = {0.f, 0.f, 0.f, 0.f};          // four sums side by side, added in a fixed order
 #pragma unroll
-            for (int k = 0; k < SS_NS; ++k) {
-                if (n0 + k < N) {
-                    S[k] = fmaf(exp2f(dtv * A[k]), S[k], dx * bj[k]);
-                    y = fmaf(S[k], cj[k], y);
+                for (int k4 = 0; k4 < SS_NS / 4; ++k4) {
+                    const float4 b4 = reinterpret_cast<const float4*>(bj)[k4], c4 = reinterpret_cast<const float4*>(cj)[k4];
+                    const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cc4[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int k = 4 * k4 + e;
+                        S[k] = fmaf(exp2f(dtv * A[k]), S[k], dx * bb[e]);
+                        ys[e] = fmaf(S[k], cc4[e], ys[e]);
+                    }
+                }
+                y = (ys[0] + ys[1]) + (ys[2] + ys[3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < SS_NS; ++k) {
+                    if (n0 + k < N) {
+                        S[k] = fmaf(exp2f(dtv * A[k]), S[k], dx * bj[k]);
+                        y = fmaf(S[k], cj[k], y);
+                    }
                 }
             }
             dt_sum += dtv;
@@ -191,22 +211,26 @@ GB_API int gb_selective_scan(const void* x, long long ldx, const void* z, long l
     p.seg = seg_scratch; p.dtype = dtype; p.low_dtype = low_dtype; p.out_dtype = out_dtype; p.inner = inner; p.N = N; p.R = R; p.lpc = lpc;
     p.max_segments = (max_qlen + SS_SEGMENT - 1) / SS_SEGMENT;
     const size_t smem = size_t(SS_CH) * (2 * N + 3 * cpb) * sizeof(float);
+    const bool full = N % SS_NS == 0;
     const unsigned blocks = unsigned((inner + cpb - 1) / cpb);
     GB_REQUIRE(B <= 65535 && p.max_segments <= 65535, "gb_selective_scan: too many sequences or segments");
     if (!seg_scratch || max_qlen <= 2 * SS_SEGMENT) {
         p.mode = 0;
-        selective_scan_kernel<<<dim3(blocks, B, 1), SS_THREADS, smem, stream>>>(p);
+        if (full) selective_scan_kernel<true><<<dim3(blocks, B, 1), SS_THREADS, smem, stream>>>(p);
+        else selective_scan_kernel<false><<<dim3(blocks, B, 1), SS_THREADS, smem, stream>>>(p);
         GB_LAUNCH_OK("gb_selective_scan");
         return 0;
     }
     p.mode = 1;
-    selective_scan_kernel<<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
+    if (full) selective_scan_kernel<true><<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
+    else selective_scan_kernel<false><<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
     GB_LAUNCH_OK("gb_selective_scan (segments from zero)");
     const long long cells = (long long)inner * N;
     selective_scan_carry_kernel<<<dim3(unsigned((cells + 127) / 128), B), 128, 0, stream>>>(p);
     GB_LAUNCH_OK("gb_selective_scan (carry)");
     p.mode = 2;
-    selective_scan_kernel<<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
+    if (full) selective_scan_kernel<true><<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
+    else selective_scan_kernel<false><<<dim3(blocks, B, p.max_segments), SS_THREADS, smem, stream>>>(p);
     GB_LAUNCH_OK("gb_selective_scan (segments)");
     return 0;
 }
