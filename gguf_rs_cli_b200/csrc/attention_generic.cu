@@ -18,7 +18,8 @@
 
 #include "common.cuh"
 
-constexpr int AG_MAX_HD = 640;
+constexpr int AG_MID_HD = 640;
+constexpr int AG_MAX_HD = 1152;          // a latent row of 1,024 entries and a rotated part of 128
 constexpr int AG_WARPS = 8;
 
 // hd: entries of a query and of a key; hdv: entries of a value (and of a head's result); a value row starts
@@ -208,12 +209,14 @@ GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void*
     attention_generic_kernel<TC, MAX_HD><<<grid, AG_WARPS * 32, 0, stream>>>(                                     \
         q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, hdv, v_row, seq_of, pos, table, table_width, ring_pages, \
         (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg, gate_per_head, sink, sink_values, chunk)
-    const bool small = hd <= 256 && hdv <= 256;
+    const bool small = hd <= 256 && hdv <= 256, mid = hd <= AG_MID_HD && hdv <= AG_MID_HD;
     if (cache_dtype == GB_F32) {
         if (small) AG_LAUNCH(float, 256);
+        else if (mid) AG_LAUNCH(float, AG_MID_HD);
         else AG_LAUNCH(float, AG_MAX_HD);
     } else {
         if (small) AG_LAUNCH(__nv_bfloat16, 256);
+        else if (mid) AG_LAUNCH(__nv_bfloat16, AG_MID_HD);
         else AG_LAUNCH(__nv_bfloat16, AG_MAX_HD);
     }
 #undef AG_LAUNCH

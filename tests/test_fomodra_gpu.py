@@ -348,6 +348,23 @@ def test_sizes_that_fit_no_fast_kernel_and_values_of_one(dtype):
         assert_model(torch.cat(got), want[:at], dtype, f"odd sizes, portions {cuts[:4]}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_latent_rows_of_more_than_640_entries(dtype):
+    """A latent of 700 entries: the cached rows are longer than the general attention kernel's middle instance takes."""
+    cfg = {"architecture": "Fomodra", "vocab": 64, "width": 64, "norm": {"eps": 1e-5},
+           "layers": [{"type": "latent_attention", "mlp": None,
+                       "mixer": {"heads": 2, "dim": 8, "rot_dim": 4, "vdim": 8, "kv_rank": 700, "scale": 0.3, "mask": {"size": 40},
+                                 "rot": {"base": 100.0, "dims": 4}}}]}
+    w = make_weights(cfg, seed=4)
+    toks = torch.randint(0, 64, (90,), generator=torch.Generator().manual_seed(4)).tolist()
+    want = P.forward(cfg, as_plain(w), toks).float()
+    from gguf_rs_cli_b200.engine.step import Engine
+    eng = Engine(build(cfg, w, dtype).model, n_tokens=512, n_slots=2)
+    s = eng.open()
+    got = [eng.step([entry(s, toks[:70], range(70))]).clone()] + [eng.step([entry(s, [t], [0])]).clone() for t in toks[70:]]
+    assert_model(torch.cat(got), want, dtype, "a long latent row")
+
+
 # ------------------------------------------------------------ keys that stand out
 def spike_model(kind, size, dims=(24, 16)):
     """One layer whose attention is decided by one key: token t + 1024 is the partner of token t; its query is the key
